@@ -1,0 +1,411 @@
+/*
+ * dmc_oracle.c -- CPU restatement of demoniC's matmul (`@`) path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA backend is
+ * compared against, and the timed CPU baseline of the benchmark.  Nothing in
+ * the product library links, loads or calls it.
+ *
+ * The reference is a Rust crate and no Rust toolchain is available where this
+ * was written, so the reference's own code cannot be compiled; every function
+ * below restates one reference function in plain C and cites the file:line it
+ * follows (paths relative to the reference project root).  Parity is pinned by
+ * the known-answer tests the reference carries for this path (see
+ * tests/test_oracle_pins.py): the bf16 widen vectors, the 3x5x4 bit-identical
+ * bf16 case, the integer goldens (415, 136, 40, 30300, 6), the contraction
+ * pins and the 2560x9728 scalar-chain pin.
+ *
+ * Build: gcc -O3 -march=x86-64-v3 -ffp-contract=off -fPIC -shared -pthread
+ * `-ffp-contract=off` matters: the only fused operation allowed is the
+ * explicit fmaf() (one rounding per multiply-add), exactly the reference's
+ * `f32::mul_add`.
+ */
+#include <math.h>
+#include <pthread.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include <unistd.h>
+
+#define ORC_API __attribute__((visibility("default")))
+
+/* ---- bf16 helpers ------------------------------------------------------- */
+
+/* compiler/src/jit.rs:29224-29227 `bf16_bits_to_f32`: widen = bits << 16. */
+static inline float bf16_widen(uint16_t h) {
+    uint32_t u = (uint32_t)h << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+ORC_API float orc_bf16_bits_to_f32(uint16_t h) { return bf16_widen(h); }
+
+/* compiler/src/jit.rs:29783-29792 `dmc_f32_to_bf16`: truncation, not RNE. */
+ORC_API void orc_f32_to_bf16_trunc(const float *src, uint16_t *dst, int64_t n) {
+    for (int64_t i = 0; i < n; i++) {
+        uint32_t u;
+        memcpy(&u, src + i, 4);
+        dst[i] = (uint16_t)(u >> 16);
+    }
+}
+
+/* compiler/src/jit.rs:29760-29776 `dmc_bf16_upconvert` (arithmetic only). */
+ORC_API void orc_bf16_upconvert(const uint16_t *src, float *dst, int64_t n) {
+    for (int64_t i = 0; i < n; i++) dst[i] = bf16_widen(src[i]);
+}
+
+/* compiler/src/jit.rs:29801-29834 `dmc_bf16_transpose_2d`: [m,n] -> [n,m],
+ * 64x64 blocked, bit patterns preserved. */
+ORC_API void orc_bf16_transpose_2d(const uint16_t *s, uint16_t *d, int64_t m, int64_t n) {
+    const int64_t BLK = 64;
+    for (int64_t i0 = 0; i0 < m; i0 += BLK) {
+        int64_t i1 = i0 + BLK < m ? i0 + BLK : m;
+        for (int64_t j0 = 0; j0 < n; j0 += BLK) {
+            int64_t j1 = j0 + BLK < n ? j0 + BLK : n;
+            for (int64_t i = i0; i < i1; i++)
+                for (int64_t j = j0; j < j1; j++) d[j * m + i] = s[i * n + j];
+        }
+    }
+}
+
+/* compiler/src/gpu.rs:342-358 `fingerprint` (identical to
+ * compiler/src/jit.rs:29712-29728 `mat_fingerprint`): byte length plus a
+ * 256-point strided u64 sample folded into a 128-bit key. */
+ORC_API void orc_fingerprint(const uint8_t *ptr, uint64_t bytes, uint64_t out[2]) {
+    uint64_t h1 = 0xcbf29ce484222325ULL ^ bytes;
+    uint64_t h2 = 0x9e3779b97f4a7c15ULL * (bytes | 1);
+    uint64_t words = bytes / 8;
+    if (words > 0) {
+        uint64_t step = words / 256;
+        if (step < 1) step = 1;
+        for (uint64_t i = 0; i < words; i += step) {
+            uint64_t v;
+            memcpy(&v, ptr + 8 * i, 8);
+            h1 = (h1 ^ v) * 0x00000100000001b3ULL;
+            uint64_t t = h2 + v;
+            t = (t << 27) | (t >> 37);
+            h2 = t * 0xff51afd7ed558ccdULL;
+        }
+    }
+    out[0] = h1;
+    out[1] = h2;
+}
+
+/* ---- reference semantics of `@` ------------------------------------------ */
+
+/* compiler/src/interp.rs:9270-9287 `gemm_f32_fma`: per output element,
+ * acc = 0f32; for kk ascending: acc = fma(a[i,kk], b[kk,j], acc). */
+ORC_API void orc_gemm_f32_fma(const float *a, const float *b, float *c,
+                              int64_t m, int64_t k, int64_t n) {
+    for (int64_t i = 0; i < m; i++)
+        for (int64_t j = 0; j < n; j++) {
+            float acc = 0.0f;
+            for (int64_t kk = 0; kk < k; kk++) acc = fmaf(a[i * k + kk], b[kk * n + j], acc);
+            c[i * n + j] = acc;
+        }
+}
+
+/* Same element order with bf16 weights widened on the fly: the interpreter's
+ * `@` applied to the widened weights (compiler/src/jit.rs:29481-29487 states
+ * the two are bit-identical). */
+ORC_API void orc_gemm_bf16_fma(const float *a, const uint16_t *b, float *c,
+                               int64_t m, int64_t k, int64_t n) {
+    for (int64_t i = 0; i < m; i++)
+        for (int64_t j = 0; j < n; j++) {
+            float acc = 0.0f;
+            for (int64_t kk = 0; kk < k; kk++)
+                acc = fmaf(a[i * k + kk], bf16_widen(b[kk * n + j]), acc);
+            c[i * n + j] = acc;
+        }
+}
+
+/* The "two-rounding" hand loop of compiler/src/jit.rs:37403-37412
+ * (s = s + a*b, product rounded before the add); used only to pin that the
+ * oracle contracts where the reference says it must. */
+ORC_API float orc_dot_two_rounding(const float *a, const float *b, int64_t k, int64_t bstride) {
+    volatile float s = 0.0f;
+    for (int64_t i = 0; i < k; i++) {
+        volatile float p = a[i] * b[i * bstride];
+        s = s + p;
+    }
+    return s;
+}
+
+/* ---- the JIT's CPU runtime kernels (timed baseline) ----------------------- */
+
+/* compiler/src/jit.rs:29448-29465 `matmul_tile`: rows [i0,i1), kk-outer /
+ * j-inner, c row zeroed first then c[j] = fma(a[kk], b[kk,j], c[j]). */
+static void matmul_tile(const float *a, const float *b, float *c,
+                        int64_t k, int64_t n, int64_t i0, int64_t i1) {
+    for (int64_t i = i0; i < i1; i++) {
+        float *crow = c + i * n;
+        for (int64_t j = 0; j < n; j++) crow[j] = 0.0f;
+        const float *arow = a + i * k;
+        for (int64_t kk = 0; kk < k; kk++) {
+            float av = arow[kk];
+            const float *brow = b + kk * n;
+            for (int64_t j = 0; j < n; j++) crow[j] = fmaf(av, brow[j], crow[j]);
+        }
+    }
+}
+
+/* compiler/src/jit.rs:29652-29672 `matmul_tile_bf16_cols` with the x86_64
+ * row pass compiler/src/jit.rs:29594-29599 (`bf16_fma_row`; the NEON 4-row
+ * pass is compiled out off aarch64): columns [j0,j1) of one output row. */
+static void matmul_tile_bf16_cols(const float *a, const uint16_t *b, float *c,
+                                  int64_t k, int64_t n, int64_t j0, int64_t j1) {
+    for (int64_t j = j0; j < j1; j++) c[j] = 0.0f;
+    for (int64_t kk = 0; kk < k; kk++) {
+        float av = a[kk];
+        const uint16_t *brow = b + kk * n;
+        for (int64_t j = j0; j < j1; j++) c[j] = fmaf(av, bf16_widen(brow[j]), c[j]);
+    }
+}
+
+/* compiler/src/jit.rs:29674-29681 `matmul_tile_bf16`. */
+static void matmul_tile_bf16(const float *a, const uint16_t *b, float *c,
+                             int64_t k, int64_t n, int64_t i0, int64_t i1) {
+    for (int64_t i = i0; i < i1; i++) matmul_tile_bf16_cols(a + i * k, b, c + i * n, k, n, 0, n);
+}
+
+typedef struct {
+    const float *a;
+    const void *b;
+    float *c;
+    int64_t k, n, lo, hi;
+    int kind; /* 0: f32 rows, 1: bf16 rows, 2: bf16 column range */
+} job_t;
+
+static void *job_main(void *p) {
+    job_t *j = (job_t *)p;
+    if (j->kind == 0) matmul_tile(j->a, (const float *)j->b, j->c, j->k, j->n, j->lo, j->hi);
+    else if (j->kind == 1) matmul_tile_bf16(j->a, (const uint16_t *)j->b, j->c, j->k, j->n, j->lo, j->hi);
+    else matmul_tile_bf16_cols(j->a, (const uint16_t *)j->b, j->c, j->k, j->n, j->lo, j->hi);
+    return NULL;
+}
+
+static int host_threads_cap = 0; /* 0 = ask the OS */
+
+/* `available_parallelism().clamp(1,16)` of compiler/src/jit.rs:29476. */
+static int64_t parallelism_cap(void) {
+    long p = host_threads_cap > 0 ? host_threads_cap : sysconf(_SC_NPROCESSORS_ONLN);
+    if (p < 1) p = 1;
+    if (p > 16) p = 16;
+    return p;
+}
+
+ORC_API void orc_set_thread_cap(int cap) { host_threads_cap = cap; }
+
+/* compiler/src/jit.rs:29471-29479 `matmul_threads`. */
+ORC_API int64_t orc_matmul_threads(int64_t m, int64_t k, int64_t n) {
+    unsigned __int128 macs = (unsigned __int128)m * (unsigned __int128)k * (unsigned __int128)n;
+    if (macs < ((unsigned __int128)1 << 20) || m < 2) return 1;
+    int64_t cap = parallelism_cap();
+    return cap < m ? cap : m;
+}
+
+static void run_jobs(job_t *jobs, int nj) {
+    pthread_t th[64];
+    for (int i = 0; i < nj; i++) pthread_create(&th[i], NULL, job_main, &jobs[i]);
+    for (int i = 0; i < nj; i++) pthread_join(th[i], NULL);
+}
+
+/* compiler/src/jit.rs:29415-29441 `dmc_matmul_par`: f32, rows split over
+ * `matmul_threads` workers. */
+ORC_API void orc_dmc_matmul_par(const float *a, const float *b, float *c,
+                                int64_t m, int64_t k, int64_t n) {
+    if (m == 0 || n == 0) return;
+    int64_t workers = orc_matmul_threads(m, k, n);
+    if (workers <= 1) { matmul_tile(a, b, c, k, n, 0, m); return; }
+    int64_t chunk = (m + workers - 1) / workers;
+    job_t jobs[64];
+    int nj = 0;
+    for (int64_t i0 = 0; i0 < m; i0 += chunk) {
+        int64_t i1 = i0 + chunk < m ? i0 + chunk : m;
+        jobs[nj++] = (job_t){a, b, c, k, n, i0, i1, 0};
+    }
+    run_jobs(jobs, nj);
+}
+
+/* Column-split ways of the m==1 decode GEMV, compiler/src/jit.rs:29527-29529:
+ * 4-way at >= 16 MiB of weights, 2-way at >= 2 MiB, else serial. */
+ORC_API int64_t orc_bf16_colsplit_ways(int64_t k, int64_t n) {
+    int64_t bytes = k * n * 2;
+    return bytes >= (16 << 20) ? 4 : bytes >= (2 << 20) ? 2 : 1;
+}
+
+/* compiler/src/jit.rs:29488-29566 `dmc_matmul_bf16`: the CPU bf16 decode
+ * GEMV/GEMM with its thread policy (m==1: 32-column-aligned column split;
+ * m>=2: row bands). */
+ORC_API void orc_dmc_matmul_bf16(const float *a, const uint16_t *b, float *c,
+                                 int64_t m, int64_t k, int64_t n) {
+    if (m == 0 || n == 0) return;
+    job_t jobs[64];
+    int nj = 0;
+    if (m == 1) {
+        int64_t ways = orc_bf16_colsplit_ways(k, n);
+        if (ways == 1) { matmul_tile_bf16(a, b, c, k, n, 0, 1); return; }
+        int64_t chunk = (((n + ways - 1) / ways) + 31) & ~(int64_t)31;
+        for (int64_t j0 = 0; j0 < n; j0 += chunk) {
+            int64_t j1 = j0 + chunk < n ? j0 + chunk : n;
+            jobs[nj++] = (job_t){a, b, c, k, n, j0, j1, 2};
+        }
+        run_jobs(jobs, nj);
+        return;
+    }
+    int64_t workers = orc_matmul_threads(m, k, n);
+    if (workers <= 1) { matmul_tile_bf16(a, b, c, k, n, 0, m); return; }
+    int64_t chunk = (m + workers - 1) / workers;
+    for (int64_t i0 = 0; i0 < m; i0 += chunk) {
+        int64_t i1 = i0 + chunk < m ? i0 + chunk : m;
+        jobs[nj++] = (job_t){a, b, c, k, n, i0, i1, 1};
+    }
+    run_jobs(jobs, nj);
+}
+
+/* compiler/src/gpu.rs:384-391 `cpu_bf16_gemm_batched`: `batch` m==1 slices
+ * at affine offsets ls (f32 elems) / rs (u16 elems); out contiguous n per
+ * slice.  Uses the plain serial kernel of compiler/src/gpu.rs:366-380. */
+ORC_API void orc_bf16_gemv_batched(const float *a, const uint16_t *b, float *c,
+                                   int64_t k, int64_t n, int64_t batch, int64_t ls, int64_t rs) {
+    for (int64_t z = 0; z < batch; z++) matmul_tile_bf16(a + z * ls, b + z * rs, c + z * n, k, n, 0, 1);
+}
+
+/* compiler/src/jit.rs:20525-20712 inline `simd_matmul`: the default f32 GEMV
+ * kernel (m==1 never leaves it without --blas).  16 output columns are held in
+ * registers across the whole k loop, then the next 16; b is re-walked with a
+ * stride of n floats per k.  Same numbers as orc_gemm_f32_fma; different
+ * memory behaviour, which is what the timed baseline needs.  Requires
+ * n % 4 == 0 (compiler/src/jit.rs:20815). */
+ORC_API void orc_simd_matmul_f32(const float *a, const float *b, float *c,
+                                 int64_t m, int64_t k, int64_t n) {
+    for (int64_t i = 0; i < m; i++) {
+        const float *arow = a + i * k;
+        int64_t j = 0;
+        for (; j + 16 <= n; j += 16) {
+            float acc[16];
+            for (int t = 0; t < 16; t++) acc[t] = 0.0f;
+            for (int64_t kk = 0; kk < k; kk++) {
+                float av = arow[kk];
+                const float *bp = b + kk * n + j;
+                for (int t = 0; t < 16; t++) acc[t] = fmaf(av, bp[t], acc[t]);
+            }
+            for (int t = 0; t < 16; t++) c[i * n + j + t] = acc[t];
+        }
+        for (; j + 4 <= n; j += 4) {
+            float acc[4] = {0, 0, 0, 0};
+            for (int64_t kk = 0; kk < k; kk++) {
+                float av = arow[kk];
+                const float *bp = b + kk * n + j;
+                for (int t = 0; t < 4; t++) acc[t] = fmaf(av, bp[t], acc[t]);
+            }
+            for (int t = 0; t < 4; t++) c[i * n + j + t] = acc[t];
+        }
+    }
+}
+
+/* compiler/src/interp.rs:9330-9374 batched `@` with NumPy-style broadcast of
+ * the leading dims.  Batch shapes are given right-aligned, already padded to
+ * a common rank `br` with 1s. */
+ORC_API void orc_matmul_broadcast_f32(const float *a, const int64_t *ab,
+                                      const float *b, const int64_t *bb,
+                                      int64_t br, int64_t m, int64_t k, int64_t n, float *out) {
+    int64_t ob[8], total = 1;
+    for (int64_t i = 0; i < br; i++) { ob[i] = ab[i] > bb[i] ? ab[i] : bb[i]; total *= ob[i]; }
+    for (int64_t p = 0; p < total; p++) {
+        int64_t rem = p, ai = 0, bi = 0, as = 1, bs = 1;
+        for (int64_t ax = br - 1; ax >= 0; ax--) {
+            int64_t coord = rem % ob[ax];
+            rem /= ob[ax];
+            if (ab[ax] > 1) ai += coord * as;
+            if (bb[ax] > 1) bi += coord * bs;
+            as *= ab[ax];
+            bs *= bb[ax];
+        }
+        orc_gemm_f32_fma(a + ai * m * k, b + bi * k * n, out + p * m * n, m, k, n);
+    }
+}
+
+/* ---- decode-step companions (f32 forms the JIT emits) --------------------- */
+
+/* compiler/src/jit.rs:23776-23847 `rms_norm` f32 lowering: sequential sum of
+ * x*x in f32, /d, +eps, sqrt, then x * g * (1/denom).
+ * Interpreter form: compiler/src/interp.rs:13559-13590 (f64). */
+ORC_API void orc_rms_norm_f32(const float *x, const float *g, float *y, int64_t d, float eps) {
+    float ss = 0.0f;
+    for (int64_t i = 0; i < d; i++) ss = ss + x[i] * x[i];
+    float denom = sqrtf(ss / (float)d + eps);
+    float inv = 1.0f / denom;
+    for (int64_t i = 0; i < d; i++) y[i] = x[i] * g[i] * inv;
+}
+
+/* compiler/src/interp.rs:13559-13590 in f64 (the interpreter's own rounding:
+ * (x/denom)*g, result rounded to f32). */
+ORC_API void orc_rms_norm_f64(const float *x, const float *g, float *y, int64_t d, double eps) {
+    double ss = 0.0;
+    for (int64_t i = 0; i < d; i++) ss += (double)x[i] * (double)x[i];
+    double denom = sqrt(ss / (double)d + eps);
+    for (int64_t i = 0; i < d; i++) y[i] = (float)(((double)x[i] / denom) * (double)g[i]);
+}
+
+/* compiler/src/interp.rs:13636-13678 `builtin_rope`: pairs (2i, 2i+1) of the
+ * last axis, one row of x [d] against cos/sin rows [d/2]. */
+ORC_API void orc_rope_row(const float *x, const float *cs, const float *sn, float *y, int64_t d) {
+    for (int64_t i = 0; i < d / 2; i++) {
+        float xa = x[2 * i], xb = x[2 * i + 1];
+        y[2 * i] = xa * cs[i] - xb * sn[i];
+        y[2 * i + 1] = xa * sn[i] + xb * cs[i];
+    }
+}
+
+/* compiler/src/interp.rs:13451-13489 `builtin_softmax` over one row (max
+ * subtract, fully-masked row -> 0). */
+ORC_API void orc_softmax_row(const float *x, float *y, int64_t n) {
+    double mx = -INFINITY;
+    for (int64_t i = 0; i < n; i++) if (x[i] > mx) mx = x[i];
+    double sum = 0.0;
+    for (int64_t i = 0; i < n; i++) {
+        double e = (mx == -INFINITY) ? 0.0 : ((double)x[i] == mx ? 1.0 : exp((double)x[i] - mx));
+        y[i] = (float)e;
+        sum += (double)y[i];
+    }
+    for (int64_t i = 0; i < n; i++) y[i] = sum == 0.0 ? 0.0f : (float)((double)y[i] / sum);
+}
+
+/* compiler/src/interp.rs:13418 `silu` = x / (1 + e^-x). */
+ORC_API float orc_silu(float x) { return (float)((double)x / (1.0 + exp(-(double)x))); }
+
+/* Decode attention for one head against a KV cache of `len` rows:
+ * scores = q.K^T (compiler/src/jit.rs:20303-20407 `lower_kv_scores`, fmul+fadd
+ * in f32, ascending), scaled by 1/sqrt(d) (compiler/src/interp.rs:13707),
+ * softmax, then p.V (compiler/src/jit.rs:20414-20506 `lower_kv_output`). */
+ORC_API void orc_kv_attention_head(const float *q, const float *kc, const float *vc,
+                                   float *out, float *scratch, int64_t len, int64_t d) {
+    float scale = (float)(1.0 / sqrt((double)d));
+    for (int64_t t = 0; t < len; t++) {
+        float s = 0.0f;
+        for (int64_t i = 0; i < d; i++) s = s + q[i] * kc[t * d + i];
+        scratch[t] = s * scale;
+    }
+    orc_softmax_row(scratch, scratch, len);
+    for (int64_t i = 0; i < d; i++) {
+        float s = 0.0f;
+        for (int64_t t = 0; t < len; t++) s = s + scratch[t] * vc[t * d + i];
+        out[i] = s;
+    }
+}
+
+/* compiler/src/interp.rs:13494-13516 `builtin_embed`: ids clamp to [0, V-1]. */
+ORC_API void orc_embed_bf16(const uint16_t *vocab, int64_t v, int64_t d, int64_t id, float *out) {
+    if (id < 0) id = 0;
+    if (id > v - 1) id = v - 1;
+    for (int64_t i = 0; i < d; i++) out[i] = bf16_widen(vocab[id * d + i]);
+}
+
+/* compiler/src/interp.rs:13529-13538 scalar argmax: first strict maximum. */
+ORC_API int64_t orc_argmax(const float *x, int64_t n) {
+    int64_t best = 0;
+    double bv = -INFINITY;
+    for (int64_t i = 0; i < n; i++) if ((double)x[i] > bv) { bv = x[i]; best = i; }
+    return best;
+}
