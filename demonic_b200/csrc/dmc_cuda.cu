@@ -1,0 +1,561 @@
+// dmc_cuda.cu -- context, resident-weight registry, staging and the C ABI of
+// libdmc_cuda.so (declared in include/dmc_cuda.h).  The structure answers the
+// reference's Metal runtime (compiler/src/gpu.rs:186-325, 476-660): weights
+// stay on the device keyed by content, the small activation and output vectors
+// cross per call through reused staging, deferred calls queue on one stream.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "runtime.h"
+
+namespace dmc {
+
+namespace {
+Context g_ctx;
+Tuning g_tuning;
+std::mutex g_mutex;
+int g_status = DMC_CUDA_OK;
+char g_msg[512] = "";
+}  // namespace
+
+Context &ctx() { return g_ctx; }
+Tuning &tuning() { return g_tuning; }
+std::mutex &ctx_mutex() { return g_mutex; }
+int status() { return g_status; }
+
+int fail(int code, const char *fmt, ...) {
+    if (g_status == DMC_CUDA_OK) {
+        g_status = code;
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(g_msg, sizeof(g_msg), fmt, ap);
+        va_end(ap);
+        if (getenv("DMC_CUDA_DEBUG")) fprintf(stderr, "[dmc_cuda] error %d: %s\n", code, g_msg);
+    }
+    return code;
+}
+
+// Content fingerprint of a weight buffer: byte length plus a 256-point strided
+// sample folded into a 128-bit key -- the reference's residency key
+// (compiler/src/gpu.rs:342-358), kept bit-compatible so a weight re-materialised
+// at a fresh host address every decode step still hits.
+static FpKey fingerprint(const uint8_t *ptr, size_t bytes) {
+    uint64_t h1 = 0xcbf29ce484222325ULL ^ (uint64_t)bytes;
+    uint64_t h2 = 0x9e3779b97f4a7c15ULL * ((uint64_t)bytes | 1);
+    size_t words = bytes / 8;
+    if (words > 0) {
+        size_t step = words / 256;
+        if (step < 1) step = 1;
+        for (size_t i = 0; i < words; i += step) {
+            uint64_t v;
+            memcpy(&v, ptr + 8 * i, 8);
+            h1 = (h1 ^ v) * 0x00000100000001b3ULL;
+            uint64_t t = h2 + v;
+            t = (t << 27) | (t >> 37);
+            h2 = t * 0xff51afd7ed558ccdULL;
+        }
+    }
+    return FpKey{h1, h2, (uint64_t)bytes};
+}
+
+static int init_locked(int device) {
+    Context &c = g_ctx;
+    if (c.ready) return DMC_CUDA_OK;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+        cudaGetLastError();
+        return fail(DMC_CUDA_ERR_NO_DEVICE, "no CUDA device is available");
+    }
+    if (device < 0) {
+        const char *env = getenv("DMC_CUDA_DEVICE");
+        if (env) device = atoi(env);
+        else if (cudaGetDevice(&device) != cudaSuccess) device = 0;
+    }
+    if (device >= count) return fail(DMC_CUDA_ERR_BAD_ARG, "device %d of %d does not exist", device, count);
+    DMC_CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    DMC_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major < 10)
+        return fail(DMC_CUDA_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only",
+                    device, prop.major, prop.minor);
+    c.device = device;
+    c.sm_count = prop.multiProcessorCount;
+    DMC_CUDA_TRY(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+    c.ready = true;
+    return DMC_CUDA_OK;
+}
+
+int ensure_init() {
+    if (g_ctx.ready) {
+        int cur = -1;
+        if (cudaGetDevice(&cur) == cudaSuccess && cur != g_ctx.device) cudaSetDevice(g_ctx.device);
+        return g_status;
+    }
+    return init_locked(-1);
+}
+
+// ---- staging ---------------------------------------------------------------------
+
+static int flush_locked();
+
+static int grow_pair(char **h, char **d, size_t *cap, size_t need) {
+    if (need <= *cap) return DMC_CUDA_OK;
+    // deferred calls still point into the old buffers: materialise them first
+    int rc = flush_locked();
+    if (rc) return rc;
+    size_t ncap = *cap ? *cap : (size_t)256 << 10;
+    while (ncap < need) ncap *= 2;
+    if (*h) cudaFreeHost(*h);
+    if (*d) cudaFree(*d);
+    *h = nullptr;
+    *d = nullptr;
+    *cap = 0;
+    DMC_CUDA_TRY(cudaMallocHost((void **)h, ncap));
+    DMC_CUDA_TRY(cudaMalloc((void **)d, ncap));
+    *cap = ncap;
+    return DMC_CUDA_OK;
+}
+
+static bool overlaps_pending(uintptr_t p, size_t bytes) {
+    for (const PendingReadback &r : g_ctx.pending) {
+        uintptr_t d0 = (uintptr_t)r.dst;
+        if (p < d0 + r.elems * 4 && d0 < p + bytes) return true;
+    }
+    return false;
+}
+
+// Wait for the stream and perform every deferred host readback
+// (compiler/src/gpu.rs:306-316 `flush_pending`).
+static int flush_locked() {
+    Context &c = g_ctx;
+    if (!c.ready) return g_status;
+    if (c.pending.empty() && c.x_off == 0 && c.y_off == 0) return g_status;
+    DMC_CUDA_TRY(cudaStreamSynchronize(c.stream));
+    for (const PendingReadback &r : c.pending) memcpy(r.dst, r.src, r.elems * sizeof(float));
+    c.pending.clear();
+    c.x_off = 0;
+    c.y_off = 0;
+    return g_status;
+}
+
+// ---- resident weights ---------------------------------------------------------------
+
+static int resident_weight(uintptr_t r, size_t bytes, void **dev) {
+    Context &c = g_ctx;
+    for (const RegisteredRange &rg : c.registered) {
+        if (r >= rg.host && r + bytes <= rg.host + rg.bytes) {
+            *dev = (char *)rg.dev + (r - rg.host);
+            return DMC_CUDA_OK;
+        }
+    }
+    FpKey key = fingerprint((const uint8_t *)r, bytes);
+    auto it = c.by_fingerprint.find(key);
+    if (it != c.by_fingerprint.end()) {
+        *dev = it->second;
+        return DMC_CUDA_OK;
+    }
+    if (c.by_fingerprint.size() > 2048) {  // same safety valve as compiler/src/gpu.rs:266
+        DMC_CUDA_TRY(cudaStreamSynchronize(c.stream));
+        for (auto &kv : c.by_fingerprint) cudaFree(kv.second);
+        c.by_fingerprint.clear();
+        c.resident_bytes = 0;
+        for (const RegisteredRange &rg : c.registered) c.resident_bytes += (int64_t)rg.bytes;
+    }
+    void *d = nullptr;
+    DMC_CUDA_TRY(cudaMalloc(&d, bytes ? bytes : 16));
+    cudaError_t e = cudaMemcpy(d, (const void *)r, bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(d);
+        return fail(DMC_CUDA_ERR_CUDA, "weight upload failed: %s", cudaGetErrorString(e));
+    }
+    if (getenv("DMC_CUDA_DEBUG"))
+        fprintf(stderr, "[dmc_cuda] upload #%zu %zu MB\n", c.by_fingerprint.size() + 1, bytes >> 20);
+    c.by_fingerprint.emplace(key, d);
+    c.resident_bytes += (int64_t)bytes;
+    *dev = d;
+    return DMC_CUDA_OK;
+}
+
+// ---- the shared host-pointer path (compiler/src/gpu.rs:479-660 `gpu_run`) ------------
+
+struct HostCall {
+    const float *l;
+    const void *r;
+    float *out;
+    int64_t m, k, n, batch, ls, rs;
+    int layout, wdtype;
+    bool defer;
+    bool resident;  // keep r on the device across calls
+};
+
+static int run_host_call(const HostCall &h) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_status) return g_status;  // sticky: nothing runs after a failure
+    if (h.m < 0 || h.k < 0 || h.n < 0 || h.batch < 0 || h.ls < 0 || h.rs < 0)
+        return fail(DMC_CUDA_ERR_BAD_ARG, "matmul: negative size (m=%lld k=%lld n=%lld batch=%lld ls=%lld rs=%lld)",
+                    (long long)h.m, (long long)h.k, (long long)h.n, (long long)h.batch, (long long)h.ls,
+                    (long long)h.rs);
+    if (h.m == 0 || h.n == 0 || h.batch == 0) return DMC_CUDA_OK;  // compiler/src/gpu.rs:402, 425
+    if (!h.l || !h.r || !h.out) return fail(DMC_CUDA_ERR_BAD_ARG, "matmul: null operand pointer");
+    if (h.batch > 1 && h.m != 1)
+        return fail(DMC_CUDA_ERR_UNSUPPORTED, "batched matmul takes m == 1 slices (got m=%lld)", (long long)h.m);
+    int rc = ensure_init();
+    if (rc) return rc;
+    Context &c = g_ctx;
+
+    const size_t wsz = h.wdtype == DMC_W_BF16 ? 2 : 4;
+    const size_t x_elems = (size_t)(h.batch - 1) * h.ls + (size_t)h.m * h.k;
+    const size_t y_elems = (size_t)h.batch * h.m * h.n;
+    const size_t w_elems = (size_t)(h.batch - 1) * h.rs + (size_t)h.k * h.n;
+
+    // a call that touches a deferred output materialises it first (compiler/src/gpu.rs:491-499)
+    if (!c.pending.empty() &&
+        (overlaps_pending((uintptr_t)h.l, x_elems * 4) || overlaps_pending((uintptr_t)h.r, w_elems * wsz) ||
+         overlaps_pending((uintptr_t)h.out, y_elems * 4))) {
+        rc = flush_locked();
+        if (rc) return rc;
+    }
+
+    size_t x_base = (c.x_off + 255) & ~(size_t)255;
+    size_t y_base = (c.y_off + 255) & ~(size_t)255;
+    if (x_base + x_elems * 4 > c.x_cap) {
+        rc = grow_pair(&c.h_x, &c.d_x, &c.x_cap, x_base + x_elems * 4);
+        if (rc) return rc;
+        x_base = (c.x_off + 255) & ~(size_t)255;  // a flush resets the offsets
+        y_base = (c.y_off + 255) & ~(size_t)255;
+    }
+    if (y_base + y_elems * 4 > c.y_cap) {
+        rc = grow_pair(&c.h_y, &c.d_y, &c.y_cap, y_base + y_elems * 4);
+        if (rc) return rc;
+        x_base = (c.x_off + 255) & ~(size_t)255;
+        y_base = (c.y_off + 255) & ~(size_t)255;
+    }
+
+    // weights: resident, or (f32 operand that may change between calls) uploaded now
+    void *dW = nullptr;
+    if (h.k > 0) {
+        if (h.resident) {
+            rc = resident_weight((uintptr_t)h.r, w_elems * wsz, &dW);
+            if (rc) return rc;
+        } else {
+            bool hit = false;
+            for (const RegisteredRange &rg : c.registered)
+                if ((uintptr_t)h.r >= rg.host && (uintptr_t)h.r + w_elems * wsz <= rg.host + rg.bytes) {
+                    dW = (char *)rg.dev + ((uintptr_t)h.r - rg.host);
+                    hit = true;
+                }
+            if (!hit) {
+                if (w_elems * wsz > c.tmpw_cap) {
+                    DMC_CUDA_TRY(cudaStreamSynchronize(c.stream));
+                    if (c.d_tmpw) cudaFree(c.d_tmpw);
+                    c.d_tmpw = nullptr;
+                    c.tmpw_cap = 0;
+                    DMC_CUDA_TRY(cudaMalloc((void **)&c.d_tmpw, w_elems * wsz));
+                    c.tmpw_cap = w_elems * wsz;
+                }
+                // pageable source: the copy returns once the source has been consumed
+                DMC_CUDA_TRY(cudaMemcpyAsync(c.d_tmpw, h.r, w_elems * wsz, cudaMemcpyHostToDevice, c.stream));
+                dW = c.d_tmpw;
+            }
+        }
+    }
+
+    memcpy(c.h_x + x_base, h.l, x_elems * 4);
+    DMC_CUDA_TRY(cudaMemcpyAsync(c.d_x + x_base, c.h_x + x_base, x_elems * 4, cudaMemcpyHostToDevice, c.stream));
+    rc = launch_gemv(dW, (const float *)(c.d_x + x_base), (float *)(c.d_y + y_base), h.m, h.k, h.n, h.batch,
+                     h.ls, h.rs, h.layout, h.wdtype, -1, c.stream);
+    if (rc) return rc;
+    DMC_CUDA_TRY(cudaMemcpyAsync(c.h_y + y_base, c.d_y + y_base, y_elems * 4, cudaMemcpyDeviceToHost, c.stream));
+
+    if (h.defer) {
+        c.pending.push_back(PendingReadback{(const float *)(c.h_y + y_base), h.out, y_elems});
+        c.x_off = x_base + x_elems * 4;
+        c.y_off = y_base + y_elems * 4;
+        return DMC_CUDA_OK;
+    }
+    c.pending.push_back(PendingReadback{(const float *)(c.h_y + y_base), h.out, y_elems});
+    c.x_off = x_base + x_elems * 4;  // make the flush below non-trivial even with nothing deferred
+    return flush_locked();
+}
+
+}  // namespace dmc
+
+using namespace dmc;
+
+// ---- C ABI ------------------------------------------------------------------------------
+
+extern "C" int dmc_cuda_device_count(void) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return count;
+}
+
+extern "C" int dmc_cuda_init(int device) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    return init_locked(device);
+}
+
+extern "C" void dmc_cuda_shutdown(void) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    Context &c = ctx();
+    if (!c.ready) return;
+    flush_locked();
+    cudaStreamSynchronize(c.stream);
+    for (auto &kv : c.by_fingerprint) cudaFree(kv.second);
+    c.by_fingerprint.clear();
+    for (auto &rg : c.registered) cudaFree(rg.dev);
+    c.registered.clear();
+    if (c.h_x) cudaFreeHost(c.h_x);
+    if (c.h_y) cudaFreeHost(c.h_y);
+    if (c.d_x) cudaFree(c.d_x);
+    if (c.d_y) cudaFree(c.d_y);
+    if (c.partial) cudaFree(c.partial);
+    if (c.counters) cudaFree(c.counters);
+    if (c.d_tmpw) cudaFree(c.d_tmpw);
+    cudaStreamDestroy(c.stream);
+    c = Context();
+}
+
+extern "C" int dmc_cuda_status(void) { return dmc::status(); }
+extern "C" const char *dmc_cuda_last_error(void) { return g_msg; }
+extern "C" void dmc_cuda_clear_error(void) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    g_status = DMC_CUDA_OK;
+    g_msg[0] = 0;
+    cudaGetLastError();
+}
+
+extern "C" void dmc_matmul_bf16_gpu(int64_t l, int64_t r, int64_t out, int64_t m, int64_t k, int64_t n) {
+    run_host_call(HostCall{(const float *)l, (const void *)r, (float *)out, m, k, n, 1, 0, 0, DMC_LAYOUT_KN,
+                           DMC_W_BF16, false, true});
+}
+
+extern "C" void dmc_matmul_bf16_gpu_batched(int64_t l, int64_t r, int64_t out, int64_t m, int64_t k, int64_t n,
+                                            int64_t batch, int64_t ls, int64_t rs) {
+    run_host_call(HostCall{(const float *)l, (const void *)r, (float *)out, m, k, n, batch, ls, rs, DMC_LAYOUT_KN,
+                           DMC_W_BF16, false, true});
+}
+
+extern "C" void dmc_matmul_bf16_gpu_batched_deferred(int64_t l, int64_t r, int64_t out, int64_t m, int64_t k,
+                                                     int64_t n, int64_t batch, int64_t ls, int64_t rs) {
+    run_host_call(HostCall{(const float *)l, (const void *)r, (float *)out, m, k, n, batch, ls, rs, DMC_LAYOUT_KN,
+                           DMC_W_BF16, true, true});
+}
+
+extern "C" void dmc_matmul_bf16_gpu_flush(void) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    flush_locked();
+}
+
+extern "C" void dmc_matmul_f32_gpu(int64_t l, int64_t r, int64_t out, int64_t m, int64_t k, int64_t n) {
+    run_host_call(HostCall{(const float *)l, (const void *)r, (float *)out, m, k, n, 1, 0, 0, DMC_LAYOUT_KN,
+                           DMC_W_F32, false, false});
+}
+
+extern "C" void dmc_matmul_bf16_gpu_nt(int64_t l, int64_t w, int64_t out, int64_t m, int64_t k, int64_t n) {
+    run_host_call(HostCall{(const float *)l, (const void *)w, (float *)out, m, k, n, 1, 0, 0, DMC_LAYOUT_NK,
+                           DMC_W_BF16, false, true});
+}
+
+extern "C" int dmc_cuda_matmul_selected(int flag_on, uint32_t deterministic_depth, int64_t m, int64_t k,
+                                        int64_t n, int64_t batch, int rhs_bf16) {
+    if (!flag_on || deterministic_depth != 0) return 0;
+    if (m <= 0 || k <= 0 || n <= 0 || batch <= 0) return 0;
+    const __int128 macs1 = (__int128)m * k * n;
+    if (!rhs_bf16) return macs1 >= ((__int128)1 << 17);
+    if (batch == 1) return (__int128)k * n >= 4000000;
+    return batch <= 65536 && macs1 * batch >= 1000000;
+}
+
+extern "C" int dmc_cuda_register_weight(int64_t ptr, int64_t bytes, int wdtype) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return dmc::status();
+    if (!ptr || bytes <= 0 || (wdtype != DMC_W_BF16 && wdtype != DMC_W_F32))
+        return fail(DMC_CUDA_ERR_BAD_ARG, "register_weight: bad range or type");
+    int rc = ensure_init();
+    if (rc) return rc;
+    Context &c = ctx();
+    for (const RegisteredRange &rg : c.registered)
+        if ((uintptr_t)ptr < rg.host + rg.bytes && rg.host < (uintptr_t)ptr + (size_t)bytes)
+            return fail(DMC_CUDA_ERR_BAD_ARG, "register_weight: range overlaps a registered range");
+    void *d = nullptr;
+    DMC_CUDA_TRY(cudaMalloc(&d, (size_t)bytes));
+    cudaError_t e = cudaMemcpy(d, (const void *)ptr, (size_t)bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(d);
+        return fail(DMC_CUDA_ERR_CUDA, "register_weight: upload failed: %s", cudaGetErrorString(e));
+    }
+    c.registered.push_back(RegisteredRange{(uintptr_t)ptr, (size_t)bytes, d, wdtype});
+    c.resident_bytes += bytes;
+    return DMC_CUDA_OK;
+}
+
+extern "C" int dmc_cuda_unregister_weight(int64_t ptr) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    Context &c = ctx();
+    for (size_t i = 0; i < c.registered.size(); ++i)
+        if (c.registered[i].host == (uintptr_t)ptr) {
+            cudaStreamSynchronize(c.stream);
+            cudaFree(c.registered[i].dev);
+            c.resident_bytes -= (int64_t)c.registered[i].bytes;
+            c.registered.erase(c.registered.begin() + i);
+            return DMC_CUDA_OK;
+        }
+    return DMC_CUDA_ERR_BAD_ARG;  // not an error worth making sticky
+}
+
+extern "C" int64_t dmc_cuda_resident_count(void) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    return (int64_t)(ctx().by_fingerprint.size() + ctx().registered.size());
+}
+extern "C" int64_t dmc_cuda_resident_bytes(void) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    return ctx().resident_bytes;
+}
+extern "C" void dmc_cuda_drop_resident(void) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    Context &c = ctx();
+    if (!c.ready) return;
+    cudaStreamSynchronize(c.stream);
+    for (auto &kv : c.by_fingerprint) cudaFree(kv.second);
+    c.by_fingerprint.clear();
+    c.resident_bytes = 0;
+    for (const RegisteredRange &rg : c.registered) c.resident_bytes += (int64_t)rg.bytes;
+}
+
+extern "C" int dmc_cuda_set_param(const char *name, int64_t value) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    Tuning &t = tuning();
+    if (!strcmp(name, "pdl")) t.pdl = (int)value;
+    else if (!strcmp(name, "kn_ctas_per_sm")) t.kn_ctas_per_sm = (int)value;
+    else if (!strcmp(name, "kn_ksplit")) t.kn_ksplit = (int)value;
+    else if (!strcmp(name, "nk_ctas_per_sm")) t.nk_ctas_per_sm = (int)value;
+    else return DMC_CUDA_ERR_BAD_ARG;
+    return DMC_CUDA_OK;
+}
+
+// ---- device-resident path -----------------------------------------------------------------
+
+extern "C" void *dmc_cuda_dev_alloc(int64_t bytes) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status() || ensure_init()) return nullptr;
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes > 0 ? (size_t)bytes : 16);
+    if (e != cudaSuccess) {
+        fail(DMC_CUDA_ERR_OOM, "dev_alloc(%lld) failed: %s", (long long)bytes, cudaGetErrorString(e));
+        return nullptr;
+    }
+    return p;
+}
+extern "C" void dmc_cuda_dev_free(void *p) {
+    if (p) cudaFree(p);
+}
+extern "C" int dmc_cuda_h2d(void *dst, const void *src, int64_t bytes) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return dmc::status();
+    DMC_CUDA_TRY(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, ctx().stream));
+    DMC_CUDA_TRY(cudaStreamSynchronize(ctx().stream));
+    return DMC_CUDA_OK;
+}
+extern "C" int dmc_cuda_d2h(void *dst, const void *src, int64_t bytes) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return dmc::status();
+    DMC_CUDA_TRY(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToHost, ctx().stream));
+    DMC_CUDA_TRY(cudaStreamSynchronize(ctx().stream));
+    return DMC_CUDA_OK;
+}
+extern "C" int dmc_cuda_memset(void *dst, int value, int64_t bytes) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return dmc::status();
+    DMC_CUDA_TRY(cudaMemsetAsync(dst, value, (size_t)bytes, ctx().stream));
+    return DMC_CUDA_OK;
+}
+extern "C" int dmc_cuda_sync(void) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (!ctx().ready) return dmc::status();
+    DMC_CUDA_TRY(cudaStreamSynchronize(ctx().stream));
+    return dmc::status();
+}
+
+extern "C" int dmc_cuda_gemv_dev(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
+                                 int layout, int wdtype, int variant) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return dmc::status();
+    int rc = ensure_init();
+    if (rc) return rc;
+    return launch_gemv(dW, dx, dy, m, k, n, 1, 0, 0, layout, wdtype, variant, ctx().stream);
+}
+
+extern "C" double dmc_cuda_bench_items(const dmc_gemv_item *items, int count, int steps, int warmup,
+                                       int use_graph) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status() || ensure_init()) return -1.0;
+    if (!items || count <= 0 || steps <= 0 || warmup < 0) {
+        fail(DMC_CUDA_ERR_BAD_ARG, "bench_items: need count > 0, steps > 0, warmup >= 0");
+        return -1.0;
+    }
+    Context &c = ctx();
+    cudaStream_t s = c.stream;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    double us = -1.0;
+    auto one_step = [&]() -> int {
+        for (int i = 0; i < count; ++i) {
+            const dmc_gemv_item &it = items[i];
+            int rc = launch_gemv(it.W, it.x, it.y, it.m, it.k, it.n, 1, 0, 0, it.layout, it.wdtype, it.variant, s);
+            if (rc) return rc;
+        }
+        return DMC_CUDA_OK;
+    };
+    auto body = [&]() -> int {
+        // one untimed eager step: sizes the split-K scratch (nothing may allocate under capture)
+        int rc = one_step();
+        if (rc) return rc;
+        DMC_CUDA_TRY(cudaStreamSynchronize(s));
+        DMC_CUDA_TRY(cudaEventCreate(&e0));
+        DMC_CUDA_TRY(cudaEventCreate(&e1));
+        int64_t per_step = 0;
+        if (use_graph) {
+            const int64_t before = c.launches;
+            DMC_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+            rc = one_step();
+            cudaError_t ce = cudaStreamEndCapture(s, &graph);
+            if (rc) return rc;
+            DMC_CUDA_TRY(ce);
+            per_step = c.launches - before;
+            DMC_CUDA_TRY(cudaGraphInstantiate(&exec, graph, 0));
+        }
+        auto run_step = [&]() -> int {
+            if (!use_graph) return one_step();
+            DMC_CUDA_TRY(cudaGraphLaunch(exec, s));
+            c.launches += per_step;  // a replay launches the captured kernels again
+            return DMC_CUDA_OK;
+        };
+        for (int i = 0; i < warmup; ++i)
+            if ((rc = run_step())) return rc;
+        DMC_CUDA_TRY(cudaStreamSynchronize(s));
+        DMC_CUDA_TRY(cudaEventRecord(e0, s));
+        for (int i = 0; i < steps; ++i)
+            if ((rc = run_step())) return rc;
+        DMC_CUDA_TRY(cudaEventRecord(e1, s));
+        DMC_CUDA_TRY(cudaStreamSynchronize(s));
+        float ms = 0.0f;
+        DMC_CUDA_TRY(cudaEventElapsedTime(&ms, e0, e1));
+        us = (double)ms * 1000.0 / steps;
+        return DMC_CUDA_OK;
+    };
+    body();
+    if (exec) cudaGraphExecDestroy(exec);
+    if (graph) cudaGraphDestroy(graph);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    return dmc::status() ? -1.0 : us;
+}
+
+extern "C" int64_t dmc_cuda_launch_count(void) { return ctx().launches; }

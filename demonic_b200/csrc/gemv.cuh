@@ -1,0 +1,394 @@
+// gemv.cuh -- memory-bound weight-streaming GEMV kernels for sm_100a.
+//
+// Two weight layouts:
+//   KN  W[k][n], n contiguous  (`x @ W`; what the reference's builtins receive:
+//       compiler/src/gpu.rs:397-399, kernel analogue compiler/src/gpu.rs:115-153)
+//   NK  W[n][k], k contiguous  (`x @ W'` consumed without the transpose pass of
+//       compiler/src/jit.rs:29801-29834)
+// Weights are bf16 bit patterns (widen = bits << 16, compiler/src/jit.rs:29224-29227)
+// or f32; activations and outputs are f32; accumulation is f32 FMA.  The
+// summation order differs from the reference's ascending-k chain (split across
+// warps / CTAs), which the reference allows for its own GPU path
+// ("within f32 reduction-order tolerance", compiler/src/gpu.rs:35-37).
+//
+// Every weight byte is read exactly once with 128-bit streaming loads that
+// bypass L1; algorithmic traffic per GEMV is n*k*sizeof(W) + 4k + 4n bytes.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dmc {
+
+struct GemvArgs {
+    const void *W;       // weights, layout per kernel
+    const float *x;      // activations [M][K] (+ z*ls per batch slice)
+    float *y;            // outputs [M][N] (+ z*M*N per batch slice)
+    float *partial;      // split-K scratch [batch][ksplit][M][N]
+    unsigned *counters;  // split-K arrival counters [batch][colblocks], zero between launches
+    int K, N;
+    int kchunk, ksplit;  // KN: rows of k per CTA along grid.y
+    int colblocks;       // KN: CTAs along n per batch slice
+    long long ls, rs;    // batch strides in elements (x: f32, W: weight elements)
+};
+
+// ---- small device helpers ---------------------------------------------------
+
+__device__ __forceinline__ uint4 ldg_stream16(const void *p) {
+    uint4 v;
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+        : "l"(p));
+    return v;
+}
+
+// Programmatic dependent launch: everything before the wait (address setup and
+// the first weight loads, which no earlier kernel writes) overlaps the tail of
+// the previous kernel in the stream; x is only read after it.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ float bf16lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+
+template <typename WT> struct VecOf;
+template <> struct VecOf<uint16_t> { static constexpr int EPV = 8; };
+template <> struct VecOf<float> { static constexpr int EPV = 4; };
+
+// acc[e] += x * w[e] over the EPV elements of one 16-byte vector (KN layout).
+template <typename WT>
+__device__ __forceinline__ void axpy_vec(float *acc, const uint4 &w, float xv) {
+    if constexpr (sizeof(WT) == 2) {
+        acc[0] = fmaf(xv, bf16lo(w.x), acc[0]);
+        acc[1] = fmaf(xv, bf16hi(w.x), acc[1]);
+        acc[2] = fmaf(xv, bf16lo(w.y), acc[2]);
+        acc[3] = fmaf(xv, bf16hi(w.y), acc[3]);
+        acc[4] = fmaf(xv, bf16lo(w.z), acc[4]);
+        acc[5] = fmaf(xv, bf16hi(w.z), acc[5]);
+        acc[6] = fmaf(xv, bf16lo(w.w), acc[6]);
+        acc[7] = fmaf(xv, bf16hi(w.w), acc[7]);
+    } else {
+        acc[0] = fmaf(xv, __uint_as_float(w.x), acc[0]);
+        acc[1] = fmaf(xv, __uint_as_float(w.y), acc[1]);
+        acc[2] = fmaf(xv, __uint_as_float(w.z), acc[2]);
+        acc[3] = fmaf(xv, __uint_as_float(w.w), acc[3]);
+    }
+}
+
+// acc += dot(w[0..EPV), x[0..EPV)) (NK layout); xa holds x[0..4), xb x[4..8).
+template <typename WT>
+__device__ __forceinline__ float dot_vec(float acc, const uint4 &w, const float4 &xa, const float4 &xb) {
+    if constexpr (sizeof(WT) == 2) {
+        acc = fmaf(xa.x, bf16lo(w.x), acc);
+        acc = fmaf(xa.y, bf16hi(w.x), acc);
+        acc = fmaf(xa.z, bf16lo(w.y), acc);
+        acc = fmaf(xa.w, bf16hi(w.y), acc);
+        acc = fmaf(xb.x, bf16lo(w.z), acc);
+        acc = fmaf(xb.y, bf16hi(w.z), acc);
+        acc = fmaf(xb.z, bf16lo(w.w), acc);
+        acc = fmaf(xb.w, bf16hi(w.w), acc);
+    } else {
+        acc = fmaf(xa.x, __uint_as_float(w.x), acc);
+        acc = fmaf(xa.y, __uint_as_float(w.y), acc);
+        acc = fmaf(xa.z, __uint_as_float(w.z), acc);
+        acc = fmaf(xa.w, __uint_as_float(w.w), acc);
+    }
+    return acc;
+}
+
+// Split-K epilogue shared by both layouts: the CTA that arrives last at the
+// group's counter adds the partials in a fixed order (so results do not vary
+// from run to run), writes y and re-arms the counter for the next launch.
+//   partial index: ((z*ksplit + j)*M + m)*N + col
+template <int THREADS>
+__device__ __forceinline__ void splitk_finish(const GemvArgs &a, int z, int group, int M, int col0,
+                                              int ncols, int *s_last) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned t = atomicAdd(&a.counters[group], 1u);
+        *s_last = (t == (unsigned)a.ksplit - 1u);
+    }
+    __syncthreads();
+    if (!*s_last) return;
+    __threadfence();
+    for (int m = 0; m < M; ++m) {
+        for (int c = threadIdx.x; c < ncols; c += THREADS) {
+            int col = col0 + c;
+            if (col >= a.N) continue;
+            float s = 0.0f;
+            for (int j = 0; j < a.ksplit; ++j)
+                s += __ldcg(&a.partial[(((size_t)z * a.ksplit + j) * M + m) * a.N + col]);
+            a.y[((size_t)z * M + m) * a.N + col] = s;
+        }
+    }
+    if (threadIdx.x == 0) a.counters[group] = 0u;
+}
+
+// ---- KN layout ----------------------------------------------------------------
+//
+// CTA = TK warps over the same CW = 32*V*EPV columns; the warps interleave over
+// the k rows of the CTA's k range (grid.y splits K), U rows in flight per warp.
+// Per row a warp reads V contiguous 512-byte segments.  Warp partials meet in
+// shared memory; CTA partials of a split K meet in `partial` (splitk_finish).
+// grid.x = colblocks * batch, grid.y = ksplit.  Needs N % EPV == 0, rs % EPV == 0
+// and a 16-byte aligned W.
+template <int TK, int U, int V, int M, typename WT>
+__global__ void __launch_bounds__(TK * 32) gemv_kn_kernel(const GemvArgs a) {
+    constexpr int EPV = VecOf<WT>::EPV;
+    constexpr int CW = 32 * V * EPV;
+    constexpr int THREADS = TK * 32;
+    __shared__ __align__(16) float red[TK][CW];
+    __shared__ int s_last;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int cb = blockIdx.x % a.colblocks, z = blockIdx.x / a.colblocks;
+    const int K = a.K, N = a.N;
+    const WT *Wz = (const WT *)a.W + (size_t)z * a.rs;
+    const float *xz = a.x + (size_t)z * a.ls;
+    const int kbeg = blockIdx.y * a.kchunk;
+    const int kend = min(K, kbeg + a.kchunk);
+
+    int col[V];
+    bool cok[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        col[v] = cb * CW + (v * 32 + lane) * EPV;
+        cok[v] = col[v] < N;
+    }
+
+    float acc[M][V][EPV];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) acc[m][v][e] = 0.0f;
+
+    uint4 w[U][V];
+    auto load_w = [&](int k) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int kk = k + u * TK;
+#pragma unroll
+            for (int v = 0; v < V; ++v)
+                w[u][v] = (kk < kend && cok[v]) ? ldg_stream16(Wz + (size_t)kk * N + col[v])
+                                                : make_uint4(0, 0, 0, 0);
+        }
+    };
+    auto consume = [&](int k) {
+        float xv[M][U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int kk = k + u * TK;
+#pragma unroll
+            for (int m = 0; m < M; ++m) xv[m][u] = kk < kend ? __ldcg(xz + (size_t)m * K + kk) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+#pragma unroll
+                for (int v = 0; v < V; ++v) axpy_vec<WT>(acc[m][v], w[u][v], xv[m][u]);
+    };
+
+    int k = kbeg + warp;
+    if (k < kend) load_w(k);
+    griddep_launch_dependents();
+    griddep_wait();
+    if (k < kend) {
+        consume(k);
+        k += TK * U;
+    }
+    for (; k < kend; k += TK * U) {
+        load_w(k);
+        consume(k);
+    }
+
+    // warps -> CTA, one x row at a time (keeps shared memory at TK*CW floats)
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        if (m) __syncthreads();
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            float4 *dst = reinterpret_cast<float4 *>(&red[warp][(v * 32 + lane) * EPV]);
+            dst[0] = make_float4(acc[m][v][0], acc[m][v][1], acc[m][v][2], acc[m][v][3]);
+            if constexpr (EPV == 8)
+                dst[1] = make_float4(acc[m][v][4], acc[m][v][5], acc[m][v][6], acc[m][v][7]);
+        }
+        __syncthreads();
+        for (int c = threadIdx.x; c < CW; c += THREADS) {
+            const int cc = cb * CW + c;
+            if (cc >= N) continue;
+            float s = 0.0f;
+#pragma unroll
+            for (int t = 0; t < TK; ++t) s += red[t][c];
+            if (a.ksplit == 1)
+                a.y[((size_t)z * M + m) * N + cc] = s;
+            else
+                a.partial[(((size_t)z * a.ksplit + blockIdx.y) * M + m) * N + cc] = s;
+        }
+    }
+    if (a.ksplit > 1) splitk_finish<THREADS>(a, z, z * a.colblocks + cb, M, cb * CW, CW, &s_last);
+}
+
+// Any-shape fallback (odd n, unaligned strides): one column per thread, the
+// TK warps of a CTA split k, partials meet in shared memory.  Not a bandwidth
+// kernel; it exists so no shape ever leaves the GPU.  Reference analogue:
+// `gemv_bf16_tiled2d`, compiler/src/gpu.rs:158-183.
+template <int TK, typename WT>
+__global__ void __launch_bounds__(TK * 32) gemv_kn_generic_kernel(const GemvArgs a, int M) {
+    __shared__ float red[TK][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int cb = blockIdx.x % a.colblocks, z = blockIdx.x / a.colblocks;
+    const int n = cb * 32 + lane;
+    const WT *Wz = (const WT *)a.W + (size_t)z * a.rs;
+    const float *xz = a.x + (size_t)z * a.ls;
+    griddep_wait();
+    for (int m = 0; m < M; ++m) {
+        float acc = 0.0f;
+        if (n < a.N) {
+            for (int k = warp; k < a.K; k += TK) {
+                float wv;
+                if constexpr (sizeof(WT) == 2)
+                    wv = __uint_as_float((uint32_t)Wz[(size_t)k * a.N + n] << 16);
+                else
+                    wv = Wz[(size_t)k * a.N + n];
+                acc = fmaf(__ldcg(xz + (size_t)m * a.K + k), wv, acc);
+            }
+        }
+        if (m) __syncthreads();
+        red[warp][lane] = acc;
+        __syncthreads();
+        if (warp == 0 && n < a.N) {
+            float s = 0.0f;
+#pragma unroll
+            for (int t = 0; t < TK; ++t) s += red[t][lane];
+            a.y[((size_t)z * M + m) * a.N + n] = s;
+        }
+    }
+}
+
+// ---- NK layout ----------------------------------------------------------------
+//
+// x is staged once per CTA in shared memory (permuted so a lane's two float4
+// reads are conflict-free); each warp owns R rows at a time and streams them
+// with U 16-byte loads in flight per row (2 KB*U/4 contiguous per row per
+// step), then reduces across lanes with shuffles.  CTAs stride over row groups.
+// Needs K % EPV == 0 and a 16-byte aligned W.  Dynamic shared memory: K floats
+// rounded up to a multiple of 256.
+template <int WARPS, int R, int U, typename WT>
+__global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
+    constexpr int EPV = VecOf<WT>::EPV;
+    constexpr int THREADS = WARPS * 32;
+    extern __shared__ __align__(16) float xs[];
+    float4 *xs4 = reinterpret_cast<float4 *>(xs);
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int K = a.K, N = a.N;
+    const int nvec = K / EPV;
+    const uint4 *W4 = reinterpret_cast<const uint4 *>(a.W);
+    const int gstride = gridDim.x * WARPS;
+
+    uint4 w[R][U];
+    auto load_w = [&](int g, int c) {
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            const int row = g * R + j;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int cc = c + 32 * u;
+                w[j][u] = (row < N && cc < nvec) ? ldg_stream16(W4 + (size_t)row * nvec + cc)
+                                                 : make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    float acc[R];
+    auto consume = [&](int c) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int cc = c + 32 * u;
+            float4 xa = make_float4(0, 0, 0, 0), xb = xa;
+            if (cc < nvec) {
+                if constexpr (EPV == 8) {
+                    // block of 32 vectors = 64 float4: low halves first, then high halves
+                    const int blk = cc >> 5, l = cc & 31;
+                    xa = xs4[blk * 64 + l];
+                    xb = xs4[blk * 64 + 32 + l];
+                } else {
+                    xa = xs4[cc];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < R; ++j) acc[j] = dot_vec<WT>(acc[j], w[j][u], xa, xb);
+        }
+    };
+
+    int g = blockIdx.x * WARPS + warp;
+    const bool any = g * R < N;
+    if (any) load_w(g, lane);
+    griddep_launch_dependents();
+    griddep_wait();
+
+    // stage x (after the dependency wait: an earlier kernel may produce it)
+    {
+        const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
+        const int n4 = K / 4;
+        for (int i = threadIdx.x; i < n4; i += THREADS) {
+            float4 v = __ldcg(x4 + i);
+            if constexpr (EPV == 8) {
+                const int blk = i >> 6, idx = i & 63;
+                xs4[blk * 64 + (idx & 1) * 32 + (idx >> 1)] = v;
+            } else {
+                xs4[i] = v;
+            }
+        }
+    }
+    __syncthreads();
+
+    bool first = true;
+    for (; g * R < N; g += gstride) {
+#pragma unroll
+        for (int j = 0; j < R; ++j) acc[j] = 0.0f;
+        for (int c = lane; c < nvec; c += 32 * U) {
+            if (!first) load_w(g, c);
+            first = false;
+            consume(c);
+        }
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            float s = acc[j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            const int row = g * R + j;
+            if (lane == 0 && row < N) a.y[row] = s;
+        }
+    }
+}
+
+// Any-shape NK fallback: one warp per row, scalar loads.
+template <typename WT>
+__global__ void __launch_bounds__(256) gemv_nk_generic_kernel(const GemvArgs a, int M) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    griddep_wait();
+    if (row >= a.N) return;
+    const WT *Wr = (const WT *)a.W + (size_t)row * a.K;
+    for (int m = 0; m < M; ++m) {
+        float acc = 0.0f;
+        for (int k = lane; k < a.K; k += 32) {
+            float wv;
+            if constexpr (sizeof(WT) == 2)
+                wv = __uint_as_float((uint32_t)Wr[k] << 16);
+            else
+                wv = Wr[k];
+            acc = fmaf(__ldcg(a.x + (size_t)m * a.K + k), wv, acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) a.y[(size_t)m * a.N + row] = acc;
+    }
+}
+
+}  // namespace dmc

@@ -1,0 +1,268 @@
+// gemv_launch.cu -- kernel-configuration tables and launch planning for the GEMV kernels.
+#include <algorithm>
+#include <cstdio>
+
+#include "gemv.cuh"
+#include "runtime.h"
+
+namespace dmc {
+
+namespace {
+
+using KernelFn = void (*)(const GemvArgs);
+
+struct KnVariant {
+    const char *name;
+    int TK, U, V;
+    int ctas_per_sm;  // resident-CTA target used to size split-K
+    KernelFn bf16[4]; // M = 1, 2, 4, 8
+    KernelFn f32[4];
+};
+
+#define KN_ROW(TK, U, V, CPS)                                                                    \
+    {                                                                                            \
+        "kn_tk" #TK "_u" #U "_v" #V, TK, U, V, CPS,                                              \
+            {gemv_kn_kernel<TK, U, V, 1, uint16_t>, nullptr, nullptr, nullptr},                  \
+            {gemv_kn_kernel<TK, U, V, 1, float>, nullptr, nullptr, nullptr},                     \
+    }
+
+// Index 0 is the multi-row-capable configuration (M up to 8).
+static const KnVariant kKn[] = {
+    {"kn_tk8_u4_v1", 8, 4, 1, 4,
+     {gemv_kn_kernel<8, 4, 1, 1, uint16_t>, gemv_kn_kernel<8, 4, 1, 2, uint16_t>,
+      gemv_kn_kernel<8, 4, 1, 4, uint16_t>, gemv_kn_kernel<8, 4, 1, 8, uint16_t>},
+     {gemv_kn_kernel<8, 4, 1, 1, float>, gemv_kn_kernel<8, 4, 1, 2, float>,
+      gemv_kn_kernel<8, 4, 1, 4, float>, gemv_kn_kernel<8, 4, 1, 8, float>}},
+    KN_ROW(8, 8, 1, 4),
+    KN_ROW(8, 4, 2, 2),
+    KN_ROW(8, 8, 2, 2),
+    KN_ROW(16, 4, 1, 2),
+    KN_ROW(16, 4, 2, 1),
+    KN_ROW(16, 8, 1, 2),
+    KN_ROW(4, 8, 1, 8),
+    KN_ROW(4, 8, 2, 4),
+    KN_ROW(4, 16, 1, 6),
+    KN_ROW(8, 2, 4, 2),
+    KN_ROW(8, 16, 1, 2),
+};
+constexpr int kKnCount = sizeof(kKn) / sizeof(kKn[0]);
+
+struct NkVariant {
+    const char *name;
+    int WARPS, R, U;
+    KernelFn bf16, f32;
+};
+#define NK_ROW(WARPS, R, U)                                                       \
+    {                                                                             \
+        "nk_w" #WARPS "_r" #R "_u" #U, WARPS, R, U,                               \
+            gemv_nk_kernel<WARPS, R, U, uint16_t>, gemv_nk_kernel<WARPS, R, U, float> \
+    }
+static const NkVariant kNk[] = {
+    NK_ROW(8, 2, 4),  NK_ROW(8, 1, 4),  NK_ROW(8, 1, 8),  NK_ROW(8, 2, 8),
+    NK_ROW(8, 4, 4),  NK_ROW(16, 1, 4), NK_ROW(16, 2, 4), NK_ROW(16, 1, 8),
+    NK_ROW(4, 2, 8),  NK_ROW(4, 4, 4),  NK_ROW(8, 4, 2),  NK_ROW(16, 2, 2),
+};
+constexpr int kNkCount = sizeof(kNk) / sizeof(kNk[0]);
+
+int launch_ex(const void *fn, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, void **params) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    int nattr = 0;
+    if (tuning().pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        nattr = 1;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = nattr;
+    DMC_CUDA_TRY(cudaLaunchKernelExC(&cfg, fn, params));
+    ctx().launches++;
+    return DMC_CUDA_OK;
+}
+
+int ensure_scratch(size_t partial_bytes, size_t ncounters) {
+    Context &c = ctx();
+    if (partial_bytes > c.partial_cap) {
+        // in-flight kernels may still use the old buffer
+        DMC_CUDA_TRY(cudaStreamSynchronize(c.stream));
+        if (c.partial) cudaFree(c.partial);
+        c.partial = nullptr;
+        c.partial_cap = 0;
+        size_t cap = std::max(partial_bytes, (size_t)4 << 20);
+        DMC_CUDA_TRY(cudaMalloc(&c.partial, cap));
+        c.partial_cap = cap;
+    }
+    if (ncounters > c.counters_cap) {
+        DMC_CUDA_TRY(cudaStreamSynchronize(c.stream));
+        if (c.counters) cudaFree(c.counters);
+        c.counters = nullptr;
+        c.counters_cap = 0;
+        size_t cap = std::max(ncounters, (size_t)4096);
+        DMC_CUDA_TRY(cudaMalloc(&c.counters, cap * sizeof(unsigned)));
+        DMC_CUDA_TRY(cudaMemset(c.counters, 0, cap * sizeof(unsigned)));
+        c.counters_cap = cap;
+    }
+    return DMC_CUDA_OK;
+}
+
+// Default configuration per shape (from the B200 sweeps; see profiles/).
+int default_kn_variant(int64_t k, int64_t n) {
+    (void)k;
+    (void)n;
+    return 3;
+}
+int default_nk_variant(int64_t k, int64_t n) {
+    (void)k;
+    (void)n;
+    return 3;
+}
+
+int launch_kn(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
+              int64_t batch, int64_t ls, int64_t rs, int wdtype, int variant, cudaStream_t stream) {
+    Context &c = ctx();
+    const int epv = wdtype == DMC_W_BF16 ? 8 : 4;
+    const bool vec_ok = n % epv == 0 && rs % epv == 0 && ((uintptr_t)dW % 16) == 0;
+    GemvArgs a = {};
+    a.W = dW;
+    a.K = (int)k;
+    a.N = (int)n;
+    a.ls = ls;
+    a.rs = rs;
+    if (!vec_ok) {
+        a.x = dx;
+        a.y = dy;
+        a.ksplit = 1;
+        a.kchunk = (int)k;
+        a.colblocks = (int)((n + 31) / 32);
+        int M = (int)m;
+        void *params[] = {&a, &M};
+        const void *fn = wdtype == DMC_W_BF16 ? (const void *)gemv_kn_generic_kernel<8, uint16_t>
+                                              : (const void *)gemv_kn_generic_kernel<8, float>;
+        return launch_ex(fn, dim3((unsigned)(a.colblocks * batch)), dim3(256), 0, stream, params);
+    }
+    if (variant < 0 || variant >= kKnCount) variant = default_kn_variant(k, n);
+    // rows of x beyond what one kernel instance holds are processed in chunks
+    for (int64_t m0 = 0; m0 < m;) {
+        const int64_t left = m - m0;
+        int mi = left >= 8 ? 3 : left >= 4 ? 2 : left >= 2 ? 1 : 0;
+        const int M = 1 << mi;
+        const KnVariant &v = (M == 1) ? kKn[variant] : kKn[0];
+        KernelFn fn = wdtype == DMC_W_BF16 ? v.bf16[mi] : v.f32[mi];
+        const int cw = 32 * v.V * epv;
+        a.colblocks = (int)((n + cw - 1) / cw);
+        const int64_t base_ctas = (int64_t)a.colblocks * batch;
+        const int cps = tuning().kn_ctas_per_sm > 0 ? tuning().kn_ctas_per_sm : v.ctas_per_sm;
+        int64_t ksplit = tuning().kn_ksplit > 0 ? tuning().kn_ksplit
+                                                 : ((int64_t)c.sm_count * cps + base_ctas / 2) / base_ctas;
+        const int64_t step = (int64_t)v.TK * v.U;
+        ksplit = std::max<int64_t>(1, std::min<int64_t>(ksplit, (k + step - 1) / step));
+        ksplit = std::min<int64_t>(ksplit, 65535);
+        int64_t kchunk = (k + ksplit - 1) / ksplit;
+        kchunk = (kchunk + v.TK - 1) / v.TK * v.TK;
+        if (kchunk < 1) kchunk = v.TK;
+        ksplit = std::max<int64_t>(1, (k + kchunk - 1) / kchunk);
+        a.kchunk = (int)kchunk;
+        a.ksplit = (int)ksplit;
+        a.x = dx + m0 * k;
+        a.y = dy + m0 * n;
+        if (ksplit > 1) {
+            int rc = ensure_scratch((size_t)batch * ksplit * M * n * sizeof(float), (size_t)base_ctas);
+            if (rc) return rc;
+            a.partial = c.partial;
+            a.counters = c.counters;
+        }
+        void *params[] = {&a};
+        int rc = launch_ex((const void *)fn, dim3((unsigned)base_ctas, (unsigned)ksplit),
+                           dim3(v.TK * 32), 0, stream, params);
+        if (rc) return rc;
+        m0 += M;
+    }
+    return DMC_CUDA_OK;
+}
+
+int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
+              int wdtype, int variant, cudaStream_t stream) {
+    Context &c = ctx();
+    const int epv = wdtype == DMC_W_BF16 ? 8 : 4;
+    const size_t smem = (size_t)((k + 255) / 256 * 256) * sizeof(float);
+    const bool vec_ok = k % epv == 0 && ((uintptr_t)dW % 16) == 0 && ((uintptr_t)dx % 16) == 0 &&
+                        smem <= 200 * 1024;
+    GemvArgs a = {};
+    a.W = dW;
+    a.K = (int)k;
+    a.N = (int)n;
+    a.ksplit = 1;
+    if (!vec_ok) {
+        a.x = dx;
+        a.y = dy;
+        int M = (int)m;
+        void *params[] = {&a, &M};
+        const void *fn = wdtype == DMC_W_BF16 ? (const void *)gemv_nk_generic_kernel<uint16_t>
+                                              : (const void *)gemv_nk_generic_kernel<float>;
+        return launch_ex(fn, dim3((unsigned)((n + 7) / 8)), dim3(256), 0, stream, params);
+    }
+    if (variant < 0 || variant >= kNkCount) variant = default_nk_variant(k, n);
+    const NkVariant &v = kNk[variant];
+    KernelFn fn = wdtype == DMC_W_BF16 ? v.bf16 : v.f32;
+    static bool attr_set[2][kNkCount] = {};
+    if (!attr_set[wdtype][variant]) {
+        DMC_CUDA_TRY(cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          200 * 1024));
+        attr_set[wdtype][variant] = true;
+    }
+    int by_threads = 2048 / (v.WARPS * 32);
+    int by_smem = (int)std::max<size_t>(1, (220 * 1024) / (smem + 1024));
+    int cps = std::min(by_threads, by_smem);
+    if (tuning().nk_ctas_per_sm > 0) cps = std::min(cps, tuning().nk_ctas_per_sm);
+    const int64_t groups = (n + (int64_t)v.WARPS * v.R - 1) / ((int64_t)v.WARPS * v.R);
+    const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(groups, (int64_t)c.sm_count * cps));
+    for (int64_t mi = 0; mi < m; ++mi) {
+        a.x = dx + mi * k;
+        a.y = dy + mi * n;
+        void *params[] = {&a};
+        int rc = launch_ex((const void *)fn, dim3((unsigned)grid), dim3(v.WARPS * 32), smem, stream, params);
+        if (rc) return rc;
+    }
+    return DMC_CUDA_OK;
+}
+
+}  // namespace
+
+int launch_gemv(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
+                int64_t batch, int64_t ls, int64_t rs, int layout, int wdtype, int variant,
+                cudaStream_t stream) {
+    if (m <= 0 || n <= 0 || batch <= 0) return DMC_CUDA_OK;
+    if (k < 0 || k > INT32_MAX || n > INT32_MAX || m > INT32_MAX)
+        return fail(DMC_CUDA_ERR_BAD_ARG, "gemv: dimension out of range (m=%lld k=%lld n=%lld)",
+                    (long long)m, (long long)k, (long long)n);
+    if (wdtype != DMC_W_BF16 && wdtype != DMC_W_F32)
+        return fail(DMC_CUDA_ERR_BAD_ARG, "gemv: unknown weight type %d", wdtype);
+    if (k == 0) {  // empty contraction: the reference zeroes the row and adds nothing
+        DMC_CUDA_TRY(cudaMemsetAsync(dy, 0, (size_t)batch * m * n * sizeof(float), stream));
+        return DMC_CUDA_OK;
+    }
+    if (layout == DMC_LAYOUT_KN) return launch_kn(dW, dx, dy, m, k, n, batch, ls, rs, wdtype, variant, stream);
+    if (layout == DMC_LAYOUT_NK) {
+        if (batch != 1) return fail(DMC_CUDA_ERR_UNSUPPORTED, "gemv: batched NK layout is not offered");
+        return launch_nk(dW, dx, dy, m, k, n, wdtype, variant, stream);
+    }
+    return fail(DMC_CUDA_ERR_BAD_ARG, "gemv: unknown layout %d", layout);
+}
+
+}  // namespace dmc
+
+extern "C" int dmc_cuda_variant_count(int layout, int wdtype) {
+    (void)wdtype;
+    return layout == DMC_LAYOUT_KN ? dmc::kKnCount : layout == DMC_LAYOUT_NK ? dmc::kNkCount : 0;
+}
+
+extern "C" const char *dmc_cuda_variant_name(int layout, int wdtype, int variant) {
+    (void)wdtype;
+    if (layout == DMC_LAYOUT_KN && variant >= 0 && variant < dmc::kKnCount) return dmc::kKn[variant].name;
+    if (layout == DMC_LAYOUT_NK && variant >= 0 && variant < dmc::kNkCount) return dmc::kNk[variant].name;
+    return "";
+}

@@ -1,0 +1,98 @@
+// runtime.h -- internal interface between the translation units of libdmc_cuda.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/dmc_cuda.h"
+
+namespace dmc {
+
+struct FpKey {
+    uint64_t h1, h2, bytes;
+    bool operator==(const FpKey &o) const { return h1 == o.h1 && h2 == o.h2 && bytes == o.bytes; }
+};
+struct FpKeyHash {
+    size_t operator()(const FpKey &k) const { return (size_t)(k.h1 ^ (k.h2 * 0x9e3779b97f4a7c15ULL) ^ k.bytes); }
+};
+
+struct RegisteredRange {
+    uintptr_t host;
+    size_t bytes;
+    void *dev;
+    int wdtype;
+};
+
+struct PendingReadback {
+    const float *src;  // pinned staging
+    float *dst;        // caller's `out`
+    size_t elems;
+};
+
+struct Context {
+    int device = -1;
+    bool ready = false;
+    cudaStream_t stream = nullptr;
+    int sm_count = 148;
+
+    // activation / output staging: pinned host mirrors of device buffers, bump-allocated
+    // while deferred calls are outstanding (reference: compiler/src/gpu.rs:201-219)
+    char *h_x = nullptr, *h_y = nullptr;
+    char *d_x = nullptr, *d_y = nullptr;
+    size_t x_cap = 0, y_cap = 0, x_off = 0, y_off = 0;
+    std::vector<PendingReadback> pending;
+
+    // split-K scratch
+    float *partial = nullptr;
+    size_t partial_cap = 0;  // bytes
+    unsigned *counters = nullptr;
+    size_t counters_cap = 0;  // elements
+
+    // transient f32 operand upload buffer (dmc_matmul_f32_gpu)
+    char *d_tmpw = nullptr;
+    size_t tmpw_cap = 0;
+
+    // resident weights
+    std::unordered_map<FpKey, void *, FpKeyHash> by_fingerprint;
+    std::vector<RegisteredRange> registered;
+    int64_t resident_bytes = 0;
+
+    int64_t launches = 0;
+};
+
+// tuning knobs (dmc_cuda_set_param)
+struct Tuning {
+    int pdl = 1;            // programmatic dependent launch on the GEMV kernels
+    int kn_ctas_per_sm = 0; // 0 = per-variant default
+    int kn_ksplit = 0;      // 0 = derive from kn_ctas_per_sm
+    int nk_ctas_per_sm = 0; // 0 = per-variant default
+};
+
+Context &ctx();
+Tuning &tuning();
+std::mutex &ctx_mutex();
+
+// Record a sticky error (first one wins) and return its code.
+int fail(int code, const char *fmt, ...);
+int status();
+#define DMC_CUDA_TRY(expr)                                                                   \
+    do {                                                                                     \
+        cudaError_t e__ = (expr);                                                            \
+        if (e__ != cudaSuccess)                                                              \
+            return ::dmc::fail(e__ == cudaErrorMemoryAllocation ? DMC_CUDA_ERR_OOM           \
+                                                                : DMC_CUDA_ERR_CUDA,         \
+                               "%s failed: %s", #expr, cudaGetErrorString(e__));             \
+    } while (0)
+
+int ensure_init();  // lazy dmc_cuda_init on the current device; returns status
+
+// Launch one GEMV (all pointers on the device).  batch slices at strides ls/rs elements.
+int launch_gemv(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
+                int64_t batch, int64_t ls, int64_t rs, int layout, int wdtype, int variant,
+                cudaStream_t stream);
+
+}  // namespace dmc

@@ -1,0 +1,185 @@
+/*
+ * dmc_cuda.h -- C ABI of libdmc_cuda.so, the B200 (sm_100a) backend for
+ * demoniC's matrix-multiply operator `@` as lowered by `dmc jit`.
+ *
+ * The first group keeps the names, argument order and argument meaning of the
+ * reference's GPU builtins so the JIT binds them with a cfg swap; every
+ * parameter is an int64_t because JIT-emitted code calls them with the
+ * System V convention and all-i64 signatures (reference:
+ * compiler/src/jit.rs:5348-5445, symbol table compiler/src/jit.rs:3056-3075).
+ * Citations are paths inside the reference project.
+ *
+ * Error model.  The reference builtins have no error channel and fall back to
+ * a CPU kernel; this backend never computes on the CPU.  A failed call leaves
+ * `out` untouched and records a sticky status readable with
+ * dmc_cuda_status() / dmc_cuda_last_error(); the host turns a non-zero status
+ * into its `runtime error: ...` + exit(1) convention.
+ */
+#ifndef DMC_CUDA_H
+#define DMC_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#pragma GCC visibility push(default)
+
+/* ---- status codes -------------------------------------------------------- */
+enum {
+    DMC_CUDA_OK = 0,
+    DMC_CUDA_ERR_NO_DEVICE = 1,   /* no CUDA device / driver                  */
+    DMC_CUDA_ERR_BAD_ARG = 2,     /* negative size, null pointer, bad layout  */
+    DMC_CUDA_ERR_CUDA = 3,        /* a CUDA runtime call failed               */
+    DMC_CUDA_ERR_OOM = 4,         /* device or pinned allocation failed       */
+    DMC_CUDA_ERR_NCCL = 5,        /* NCCL missing or a collective failed      */
+    DMC_CUDA_ERR_TIMEOUT = 6,     /* a bounded device-side wait ran out       */
+    DMC_CUDA_ERR_UNSUPPORTED = 7  /* shape outside what an entry point takes  */
+};
+
+/* Weight memory layouts. */
+enum {
+    DMC_LAYOUT_KN = 0, /* W[k][n], n contiguous: `x @ W`, the reference's native order */
+    DMC_LAYOUT_NK = 1  /* W[n][k], k contiguous: `x @ W'` / "y = W.x" without the transpose pass */
+};
+
+/* Weight element types. */
+enum { DMC_W_BF16 = 0, DMC_W_F32 = 1 };
+
+/* ---- lifecycle and errors ------------------------------------------------- */
+
+/* Number of usable CUDA devices (0 when there is no driver or device).  The
+ * host asks this when the flag is parsed, to emit its `cuda-unavailable`
+ * diagnostic and stay on the CPU kernels, the way `--gpu` is handled at
+ * compiler/src/main.rs:1654-1691. Never fails. */
+int dmc_cuda_device_count(void);
+
+/* Create the context on `device` (stream, staging buffers).  Entry points
+ * below call it lazily with the current device (or DMC_CUDA_DEVICE) if the
+ * host did not.  Replaces the lazy `GpuCtx::new` of compiler/src/gpu.rs:226-257.
+ * Returns a status code. */
+int dmc_cuda_init(int device);
+
+/* Flush deferred work, free every device/pinned allocation, destroy the
+ * context.  Safe to call twice. */
+void dmc_cuda_shutdown(void);
+
+int dmc_cuda_status(void);              /* sticky: first error since the last clear */
+const char *dmc_cuda_last_error(void);  /* message for that status ("" when OK)      */
+void dmc_cuda_clear_error(void);
+
+/* ---- drop-in builtins (host pointers, reference ABI) ----------------------- */
+
+/* out[m,n] (f32) = l[m,k] (f32) @ r[k,n] (bf16 bits), f32 accumulate.
+ * Replaces `dmc_matmul_bf16_gpu`, compiler/src/gpu.rs:400-409 (same ABI as the
+ * CPU `dmc_matmul_bf16`, compiler/src/jit.rs:29488).  Unlike the reference,
+ * m > 1 also runs on the GPU.  Weights are uploaded on first sight and kept
+ * resident, keyed by the reference's content fingerprint
+ * (compiler/src/gpu.rs:342-358) or by a registered range (below). */
+void dmc_matmul_bf16_gpu(int64_t l, int64_t r, int64_t out, int64_t m, int64_t k, int64_t n);
+
+/* `batch` m==1 slices in one launch: slice z reads l + z*ls (f32 elements),
+ * r + z*rs (bf16 elements) and writes out + z*n; ls / rs may be 0 (broadcast
+ * operand).  Replaces `dmc_matmul_bf16_gpu_batched`,
+ * compiler/src/gpu.rs:421-439. */
+void dmc_matmul_bf16_gpu_batched(int64_t l, int64_t r, int64_t out, int64_t m, int64_t k, int64_t n,
+                                 int64_t batch, int64_t ls, int64_t rs);
+
+/* Same arguments; enqueues the work and returns without writing `out`.  The
+ * result is materialised by the next synchronous call or by the flush below.
+ * Replaces `dmc_matmul_bf16_gpu_batched_deferred`, compiler/src/gpu.rs:449-463. */
+void dmc_matmul_bf16_gpu_batched_deferred(int64_t l, int64_t r, int64_t out, int64_t m, int64_t k,
+                                          int64_t n, int64_t batch, int64_t ls, int64_t rs);
+
+/* Wait for all deferred calls and copy their results to their `out`.
+ * Replaces `dmc_matmul_bf16_gpu_flush`, compiler/src/gpu.rs:468-474. */
+void dmc_matmul_bf16_gpu_flush(void);
+
+/* out[m,n] = l[m,k] @ r[k,n], all f32, f32 accumulate: the GPU sibling of
+ * `dmc_matmul_par` / `dmc_matmul_blas` (compiler/src/jit.rs:29415, 29375; same
+ * six-argument ABI).  r is uploaded on every call unless its range was
+ * registered (an arbitrary f32 operand may be mutated between calls, so the
+ * sampled fingerprint is not trusted for it). */
+void dmc_matmul_f32_gpu(int64_t l, int64_t r, int64_t out, int64_t m, int64_t k, int64_t n);
+
+/* out[m,n] = l[m,k] @ w' with w[n,k] bf16 (k contiguous): consumes the weight
+ * as stored and so replaces the pair `dmc_bf16_transpose_2d` + `dmc_matmul_bf16`
+ * (compiler/src/jit.rs:29801-29834, 19425-19454) that the JIT emits for
+ * `x @ w'`. */
+void dmc_matmul_bf16_gpu_nt(int64_t l, int64_t w, int64_t out, int64_t m, int64_t k, int64_t n);
+
+/* ---- selection rule (pure, no device) -------------------------------------- */
+
+/* 1 when a matmul site with these static shapes goes to this backend: flag on,
+ * no enclosing `@deterministic`, and the work clears the offload threshold.
+ * Mirrors `blas_gemm_selected` (compiler/src/jit.rs:29346-29351) for the depth
+ * rule and the `--gpu` gates for the sizes: single GEMV needs k*n >= 4e6
+ * (compiler/src/jit.rs:20933-20934), a batched projection batch*m*k*n >= 1e6
+ * and batch <= 65536 (compiler/src/jit.rs:19912-19915).  `rhs_bf16` = 0 asks
+ * about an f32 `@` site (threshold: BLAS_MIN_MACS = 2^17, compiler/src/jit.rs:29340). */
+int dmc_cuda_matmul_selected(int flag_on, uint32_t deterministic_depth, int64_t m, int64_t k,
+                             int64_t n, int64_t batch, int rhs_bf16);
+
+/* ---- weight residency ------------------------------------------------------- */
+
+/* Upload host range [ptr, ptr+bytes) now and serve later calls whose weight
+ * pointer falls inside it from HBM without fingerprinting.  Meant for the
+ * `vault.load_npz` path (compiler/src/jit.rs:29836-29927), where the weight's
+ * address is stable.  `wdtype` is DMC_W_BF16 or DMC_W_F32.  Returns a status. */
+int dmc_cuda_register_weight(int64_t ptr, int64_t bytes, int wdtype);
+int dmc_cuda_unregister_weight(int64_t ptr);
+/* Number of resident weight buffers and their total bytes. */
+int64_t dmc_cuda_resident_count(void);
+int64_t dmc_cuda_resident_bytes(void);
+/* Drop every fingerprint-keyed resident weight (registered ranges stay). */
+void dmc_cuda_drop_resident(void);
+
+/* ---- device-resident path (no host copies) ---------------------------------- */
+
+void *dmc_cuda_dev_alloc(int64_t bytes);          /* NULL + status on failure */
+void dmc_cuda_dev_free(void *p);
+int dmc_cuda_h2d(void *dst, const void *src, int64_t bytes);   /* synchronous */
+int dmc_cuda_d2h(void *dst, const void *src, int64_t bytes);   /* synchronous */
+int dmc_cuda_memset(void *dst, int value, int64_t bytes);
+int dmc_cuda_sync(void);
+
+/* y[m,n] (f32, device) = x[m,k] (f32, device) @ W, W on device in `layout`
+ * with element type `wdtype`.  Asynchronous on the context's stream.
+ * `variant` < 0 lets the library choose the kernel configuration. */
+int dmc_cuda_gemv_dev(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
+                      int layout, int wdtype, int variant);
+
+/* One device-resident GEMV of a benchmark step (arguments of dmc_cuda_gemv_dev). */
+typedef struct dmc_gemv_item {
+    const void *W;
+    const float *x;
+    float *y;
+    int64_t m, k, n;
+    int layout, wdtype, variant;
+} dmc_gemv_item;
+
+/* Device-timed benchmark: a step is the `count` GEMVs of `items` launched back
+ * to back on the context's stream (give each shape enough distinct weight
+ * buffers that the step's working set exceeds L2).  Runs `warmup` untimed
+ * steps, then `steps` steps between one CUDA-event pair on the launching
+ * stream; with `use_graph` != 0 the step is captured once into a CUDA graph and
+ * replayed.  Returns microseconds per step (< 0 on error). */
+double dmc_cuda_bench_items(const dmc_gemv_item *items, int count, int steps, int warmup, int use_graph);
+
+/* Number of kernel configurations a layout/type offers, and a printable name. */
+int dmc_cuda_variant_count(int layout, int wdtype);
+const char *dmc_cuda_variant_name(int layout, int wdtype, int variant);
+
+/* Tuning knobs for sweeps: "pdl" (programmatic dependent launch, default 1),
+ * "kn_ctas_per_sm", "kn_ksplit", "nk_ctas_per_sm" (0 = library default). */
+int dmc_cuda_set_param(const char *name, int64_t value);
+
+/* Kernels this library has launched since the context was created. */
+int64_t dmc_cuda_launch_count(void);
+
+#pragma GCC visibility pop
+#ifdef __cplusplus
+}
+#endif
+#endif /* DMC_CUDA_H */
