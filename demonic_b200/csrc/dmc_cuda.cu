@@ -83,8 +83,21 @@ static int init_locked(int device) {
     c.device = device;
     c.sm_count = prop.multiProcessorCount;
     DMC_CUDA_TRY(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+    DMC_CUDA_TRY(cudaMallocHost((void **)&c.err_word, sizeof(int)));
+    *c.err_word = 0;
     c.ready = true;
     return DMC_CUDA_OK;
+}
+
+// A kernel whose bounded wait ran out leaves a code in the pinned error word.
+int check_device_error() {
+    Context &c = g_ctx;
+    if (c.err_word && *(volatile int *)c.err_word != 0) {
+        int code = *(volatile int *)c.err_word;
+        *c.err_word = 0;
+        return fail(DMC_CUDA_ERR_TIMEOUT, "a device-side wait ran out (code %d): the kernel gave up instead of hanging", code);
+    }
+    return g_status;
 }
 
 int ensure_init() {
@@ -133,6 +146,11 @@ static int flush_locked() {
     if (!c.ready) return g_status;
     if (c.pending.empty() && c.x_off == 0 && c.y_off == 0) return g_status;
     DMC_CUDA_TRY(cudaStreamSynchronize(c.stream));
+    if (check_device_error()) {  // results of a kernel that gave up are not delivered
+        c.pending.clear();
+        c.x_off = c.y_off = 0;
+        return g_status;
+    }
     for (const PendingReadback &r : c.pending) memcpy(r.dst, r.src, r.elems * sizeof(float));
     c.pending.clear();
     c.x_off = 0;
@@ -142,18 +160,28 @@ static int flush_locked() {
 
 // ---- resident weights ---------------------------------------------------------------
 
-static int resident_weight(uintptr_t r, size_t bytes, void **dev) {
+// Find or create the device copy of a host weight.  A single [k, n] bf16 matrix that
+// the TMA kernel can take is stored transposed ([n, k], k contiguous) so the one
+// bandwidth kernel serves it; *layout says how the returned buffer is laid out.
+// The transpose runs once per weight, on the device, at upload.
+static int resident_weight(uintptr_t r, size_t bytes, int64_t k, int64_t n, int wdtype, bool may_transpose,
+                           void **dev, int *layout) {
     Context &c = g_ctx;
+    *layout = DMC_LAYOUT_KN;
     for (const RegisteredRange &rg : c.registered) {
         if (r >= rg.host && r + bytes <= rg.host + rg.bytes) {
             *dev = (char *)rg.dev + (r - rg.host);
             return DMC_CUDA_OK;
         }
     }
+    const size_t wsz = wdtype == DMC_W_BF16 ? 2 : 4;
+    const bool transposed = may_transpose && g_tuning.store_nk && nk_fast_eligible(k, n, wdtype);
     FpKey key = fingerprint((const uint8_t *)r, bytes);
+    key.shape = transposed ? (((uint64_t)k << 32) | (uint64_t)n) : 0;
     auto it = c.by_fingerprint.find(key);
     if (it != c.by_fingerprint.end()) {
         *dev = it->second;
+        *layout = transposed ? DMC_LAYOUT_NK : DMC_LAYOUT_KN;
         return DMC_CUDA_OK;
     }
     if (c.by_fingerprint.size() > 2048) {  // same safety valve as compiler/src/gpu.rs:266
@@ -165,16 +193,31 @@ static int resident_weight(uintptr_t r, size_t bytes, void **dev) {
     }
     void *d = nullptr;
     DMC_CUDA_TRY(cudaMalloc(&d, bytes ? bytes : 16));
-    cudaError_t e = cudaMemcpy(d, (const void *)r, bytes, cudaMemcpyHostToDevice);
+    void *staging = d;
+    if (transposed) {
+        cudaError_t e = cudaMalloc(&staging, bytes);
+        if (e != cudaSuccess) {
+            cudaFree(d);
+            return fail(DMC_CUDA_ERR_OOM, "weight upload: staging allocation failed: %s", cudaGetErrorString(e));
+        }
+    }
+    cudaError_t e = cudaMemcpy(staging, (const void *)r, bytes, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess && transposed) {
+        int rc = launch_transpose(staging, d, k, n, (int)wsz, c.stream);
+        e = rc ? cudaErrorUnknown : cudaStreamSynchronize(c.stream);  // the GEMV may prefetch W before its dependency wait
+        cudaFree(staging);
+    }
     if (e != cudaSuccess) {
         cudaFree(d);
         return fail(DMC_CUDA_ERR_CUDA, "weight upload failed: %s", cudaGetErrorString(e));
     }
     if (getenv("DMC_CUDA_DEBUG"))
-        fprintf(stderr, "[dmc_cuda] upload #%zu %zu MB\n", c.by_fingerprint.size() + 1, bytes >> 20);
+        fprintf(stderr, "[dmc_cuda] upload #%zu %zu MB%s\n", c.by_fingerprint.size() + 1, bytes >> 20,
+                transposed ? " (stored k-contiguous)" : "");
     c.by_fingerprint.emplace(key, d);
     c.resident_bytes += (int64_t)bytes;
     *dev = d;
+    *layout = transposed ? DMC_LAYOUT_NK : DMC_LAYOUT_KN;
     return DMC_CUDA_OK;
 }
 
@@ -235,10 +278,14 @@ static int run_host_call(const HostCall &h) {
 
     // weights: resident, or (f32 operand that may change between calls) uploaded now
     void *dW = nullptr;
+    int layout = h.layout;
     if (h.k > 0) {
         if (h.resident) {
-            rc = resident_weight((uintptr_t)h.r, w_elems * wsz, &dW);
+            int stored = DMC_LAYOUT_KN;
+            rc = resident_weight((uintptr_t)h.r, w_elems * wsz, h.k, h.n, h.wdtype,
+                                 h.layout == DMC_LAYOUT_KN && h.batch == 1, &dW, &stored);
             if (rc) return rc;
+            if (h.layout == DMC_LAYOUT_KN) layout = stored;
         } else {
             bool hit = false;
             for (const RegisteredRange &rg : c.registered)
@@ -265,7 +312,7 @@ static int run_host_call(const HostCall &h) {
     memcpy(c.h_x + x_base, h.l, x_elems * 4);
     DMC_CUDA_TRY(cudaMemcpyAsync(c.d_x + x_base, c.h_x + x_base, x_elems * 4, cudaMemcpyHostToDevice, c.stream));
     rc = launch_gemv(dW, (const float *)(c.d_x + x_base), (float *)(c.d_y + y_base), h.m, h.k, h.n, h.batch,
-                     h.ls, h.rs, h.layout, h.wdtype, -1, c.stream);
+                     h.ls, h.rs, layout, h.wdtype, -1, c.stream);
     if (rc) return rc;
     DMC_CUDA_TRY(cudaMemcpyAsync(c.h_y + y_base, c.d_y + y_base, y_elems * 4, cudaMemcpyDeviceToHost, c.stream));
 
@@ -317,6 +364,7 @@ extern "C" void dmc_cuda_shutdown(void) {
     if (c.partial) cudaFree(c.partial);
     if (c.counters) cudaFree(c.counters);
     if (c.d_tmpw) cudaFree(c.d_tmpw);
+    if (c.err_word) cudaFreeHost(c.err_word);
     cudaStreamDestroy(c.stream);
     c = Context();
 }
@@ -435,6 +483,11 @@ extern "C" int dmc_cuda_set_param(const char *name, int64_t value) {
     else if (!strcmp(name, "kn_ctas_per_sm")) t.kn_ctas_per_sm = (int)value;
     else if (!strcmp(name, "kn_ksplit")) t.kn_ksplit = (int)value;
     else if (!strcmp(name, "nk_ctas_per_sm")) t.nk_ctas_per_sm = (int)value;
+    else if (!strcmp(name, "tma_ring_kb")) t.tma_ring_kb = (int)value;
+    else if (!strcmp(name, "tma_stage_kb")) t.tma_stage_kb = (int)value;
+    else if (!strcmp(name, "tma_ctas_per_sm")) t.tma_ctas_per_sm = (int)value;
+    else if (!strcmp(name, "store_nk")) t.store_nk = (int)value;
+    else if (!strcmp(name, "nk_default")) t.nk_default = (int)value;
     else return DMC_CUDA_ERR_BAD_ARG;
     return DMC_CUDA_OK;
 }
@@ -479,7 +532,7 @@ extern "C" int dmc_cuda_sync(void) {
     std::lock_guard<std::mutex> lock(ctx_mutex());
     if (!ctx().ready) return dmc::status();
     DMC_CUDA_TRY(cudaStreamSynchronize(ctx().stream));
-    return dmc::status();
+    return check_device_error();
 }
 
 extern "C" int dmc_cuda_gemv_dev(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,

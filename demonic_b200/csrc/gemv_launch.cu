@@ -3,6 +3,7 @@
 #include <cstdio>
 
 #include "gemv.cuh"
+#include "gemv_tma.cuh"
 #include "runtime.h"
 
 namespace dmc {
@@ -184,6 +185,97 @@ int launch_kn(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
     return DMC_CUDA_OK;
 }
 
+// ---- NK layout, TMA ring kernel ------------------------------------------------------
+
+using TmaFn = void (*)(const GemvTmaArgs);
+#define TMA_ROW(T, CW)                                                                              \
+    {gemv_nk_tma_kernel<1, CW, T>, gemv_nk_tma_kernel<2, CW, T>, gemv_nk_tma_kernel<3, CW, T>,     \
+     gemv_nk_tma_kernel<4, CW, T>, gemv_nk_tma_kernel<5, CW, T>, gemv_nk_tma_kernel<6, CW, T>,     \
+     gemv_nk_tma_kernel<7, CW, T>, gemv_nk_tma_kernel<8, CW, T>}
+static const TmaFn kTma[2][2][8] = {  // [wdtype][CW == 16][VPL - 1]
+    {TMA_ROW(uint16_t, 8), TMA_ROW(uint16_t, 16)},
+    {TMA_ROW(float, 8), TMA_ROW(float, 16)},
+};
+constexpr int kTmaVariantCw8 = kNkCount;       // variant ids after the LDG configurations
+constexpr int kTmaVariantCw16 = kNkCount + 1;
+constexpr int kNkTotal = kNkCount + 2;
+
+struct TmaPlan {
+    bool ok = false;
+    int cw = 8, vpl = 1, SR = 1, S = 2, stage_bytes = 0;
+    size_t smem = 0;
+};
+
+// Ring geometry: stages of whole rows (~tma_stage_kb each), as many as fit the ring
+// budget.  The default budget leaves room for the next kernel's CTA on the same SM,
+// so its first stages load while this kernel is still running.
+TmaPlan plan_tma(int64_t k, int64_t n, int wdtype, int want_cw, const void *dW, const float *dx) {
+    TmaPlan p;
+    const int wsz = wdtype == DMC_W_BF16 ? 2 : 4;
+    const int epv = 16 / wsz;
+    if (k % epv || ((uintptr_t)dW % 16) || ((uintptr_t)dx % 16) || n < 1) return p;
+    const int64_t nvec = k / epv;
+    if (nvec < 256) return p;  // short rows leave most lanes idle: the LDG kernel takes them
+    int cw = want_cw;
+    if (cw == 0) cw = (nvec + 255) / 256 <= 4 ? 8 : 16;
+    int vpl = (int)((nvec + cw * 32 - 1) / (cw * 32));
+    if (vpl > 8 && cw == 8) {
+        cw = 16;
+        vpl = (int)((nvec + cw * 32 - 1) / (cw * 32));
+    }
+    if (vpl > 8) return p;
+    const int64_t rowbytes = k * wsz;
+    const int64_t ring = (int64_t)(tuning().tma_ring_kb > 0 ? tuning().tma_ring_kb : 96) * 1024;
+    const int64_t stage_target = (int64_t)(tuning().tma_stage_kb > 0 ? tuning().tma_stage_kb : 32) * 1024;
+    int64_t SR = std::max<int64_t>(1, stage_target / rowbytes);
+    if (SR > 4) SR = SR / 4 * 4;
+    SR = std::min<int64_t>(SR, 32);
+    int64_t S = ring / (SR * rowbytes);
+    while (S < 2 && SR > 1) {
+        SR = std::max<int64_t>(1, SR / 2);
+        S = ring / (SR * rowbytes);
+    }
+    if (S < 2) return p;
+    S = std::min<int64_t>(S, kTmaMaxStages);
+    p.cw = cw;
+    p.vpl = vpl;
+    p.SR = (int)SR;
+    p.S = (int)S;
+    p.stage_bytes = (int)(SR * rowbytes);
+    p.smem = (size_t)S * p.stage_bytes + (size_t)S * SR * cw * sizeof(float);
+    p.ok = p.smem <= 200 * 1024;
+    return p;
+}
+
+int launch_nk_tma(const TmaPlan &p, const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
+                  int wdtype, cudaStream_t stream) {
+    Context &c = ctx();
+    TmaFn fn = kTma[wdtype][p.cw == 16][p.vpl - 1];
+    static bool attr_set[2][2][8] = {};
+    if (!attr_set[wdtype][p.cw == 16][p.vpl - 1]) {
+        DMC_CUDA_TRY(cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_set[wdtype][p.cw == 16][p.vpl - 1] = true;
+    }
+    GemvTmaArgs a = {};
+    a.W = dW;
+    a.err = c.err_word;
+    a.N = (int)n;
+    a.K = (int)k;
+    a.SR = p.SR;
+    a.S = p.S;
+    a.stage_bytes = p.stage_bytes;
+    const int64_t per_sm = tuning().tma_ctas_per_sm > 0 ? tuning().tma_ctas_per_sm : 1;
+    const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(n, (int64_t)c.sm_count * per_sm));
+    for (int64_t mi = 0; mi < m; ++mi) {
+        a.x = dx + mi * k;
+        a.y = dy + mi * n;
+        void *params[] = {&a};
+        int rc = launch_ex((const void *)fn, dim3((unsigned)grid), dim3((p.cw + 1) * 32), p.smem, stream, params);
+        if (rc) return rc;
+    }
+    return DMC_CUDA_OK;
+}
+
 int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
               int wdtype, int variant, cudaStream_t stream) {
     Context &c = ctx();
@@ -191,6 +283,12 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
     const size_t smem = (size_t)((k + 255) / 256 * 256) * sizeof(float);
     const bool vec_ok = k % epv == 0 && ((uintptr_t)dW % 16) == 0 && ((uintptr_t)dx % 16) == 0 &&
                         smem <= 200 * 1024;
+    if (variant < 0 && tuning().nk_default >= 0) variant = tuning().nk_default;
+    if (variant == kTmaVariantCw8 || variant == kTmaVariantCw16) {
+        TmaPlan p = plan_tma(k, n, wdtype, variant == kTmaVariantCw8 ? 8 : 16, dW, dx);
+        if (p.ok) return launch_nk_tma(p, dW, dx, dy, m, k, n, wdtype, stream);
+        variant = -1;  // shape outside the ring kernel: fall through to the LDG kernel
+    }
     GemvArgs a = {};
     a.W = dW;
     a.K = (int)k;
@@ -232,6 +330,24 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
 
 }  // namespace
 
+bool nk_fast_eligible(int64_t k, int64_t n, int wdtype) {
+    const int epv = wdtype == DMC_W_BF16 ? 8 : 4;
+    return n >= 1 && k >= 512 && k % epv == 0 && (size_t)((k + 255) / 256 * 256) * sizeof(float) <= 200 * 1024;
+}
+
+int launch_transpose(const void *src, void *dst, int64_t rows, int64_t cols, int elem_bytes, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return DMC_CUDA_OK;
+    dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
+    if (grid.y > 65535) return fail(DMC_CUDA_ERR_UNSUPPORTED, "transpose: more than 4M rows");
+    if (elem_bytes == 2)
+        transpose_kernel<uint16_t><<<grid, 256, 0, stream>>>((const uint16_t *)src, (uint16_t *)dst, (int)rows, (int)cols);
+    else
+        transpose_kernel<uint32_t><<<grid, 256, 0, stream>>>((const uint32_t *)src, (uint32_t *)dst, (int)rows, (int)cols);
+    DMC_CUDA_TRY(cudaGetLastError());
+    ctx().launches++;
+    return DMC_CUDA_OK;
+}
+
 int launch_gemv(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
                 int64_t batch, int64_t ls, int64_t rs, int layout, int wdtype, int variant,
                 cudaStream_t stream) {
@@ -257,12 +373,14 @@ int launch_gemv(const void *dW, const float *dx, float *dy, int64_t m, int64_t k
 
 extern "C" int dmc_cuda_variant_count(int layout, int wdtype) {
     (void)wdtype;
-    return layout == DMC_LAYOUT_KN ? dmc::kKnCount : layout == DMC_LAYOUT_NK ? dmc::kNkCount : 0;
+    return layout == DMC_LAYOUT_KN ? dmc::kKnCount : layout == DMC_LAYOUT_NK ? dmc::kNkTotal : 0;
 }
 
 extern "C" const char *dmc_cuda_variant_name(int layout, int wdtype, int variant) {
     (void)wdtype;
     if (layout == DMC_LAYOUT_KN && variant >= 0 && variant < dmc::kKnCount) return dmc::kKn[variant].name;
     if (layout == DMC_LAYOUT_NK && variant >= 0 && variant < dmc::kNkCount) return dmc::kNk[variant].name;
+    if (layout == DMC_LAYOUT_NK && variant == dmc::kTmaVariantCw8) return "nk_tma_cw8";
+    if (layout == DMC_LAYOUT_NK && variant == dmc::kTmaVariantCw16) return "nk_tma_cw16";
     return "";
 }

@@ -14,10 +14,15 @@ namespace dmc {
 
 struct FpKey {
     uint64_t h1, h2, bytes;
-    bool operator==(const FpKey &o) const { return h1 == o.h1 && h2 == o.h2 && bytes == o.bytes; }
+    uint64_t shape = 0;  // (k << 32 | n) when the device copy is stored transposed, else 0
+    bool operator==(const FpKey &o) const {
+        return h1 == o.h1 && h2 == o.h2 && bytes == o.bytes && shape == o.shape;
+    }
 };
 struct FpKeyHash {
-    size_t operator()(const FpKey &k) const { return (size_t)(k.h1 ^ (k.h2 * 0x9e3779b97f4a7c15ULL) ^ k.bytes); }
+    size_t operator()(const FpKey &k) const {
+        return (size_t)(k.h1 ^ (k.h2 * 0x9e3779b97f4a7c15ULL) ^ k.bytes ^ (k.shape * 0xff51afd7ed558ccdULL));
+    }
 };
 
 struct RegisteredRange {
@@ -61,6 +66,9 @@ struct Context {
     std::vector<RegisteredRange> registered;
     int64_t resident_bytes = 0;
 
+    // error word written by kernels whose bounded waits run out (pinned, device-visible)
+    int *err_word = nullptr;
+
     int64_t launches = 0;
 };
 
@@ -70,6 +78,11 @@ struct Tuning {
     int kn_ctas_per_sm = 0; // 0 = per-variant default
     int kn_ksplit = 0;      // 0 = derive from kn_ctas_per_sm
     int nk_ctas_per_sm = 0; // 0 = per-variant default
+    int tma_ring_kb = 0;    // shared-memory ring per CTA (0 = 96 KiB)
+    int tma_stage_kb = 0;   // target stage size (0 = 32 KiB)
+    int tma_ctas_per_sm = 0;
+    int store_nk = 1;       // keep resident [k,n] weights k-contiguous on the device
+    int nk_default = -1;    // NK variant used when the caller passes -1 (-1 = library choice)
 };
 
 Context &ctx();
@@ -94,5 +107,13 @@ int ensure_init();  // lazy dmc_cuda_init on the current device; returns status
 int launch_gemv(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
                 int64_t batch, int64_t ls, int64_t rs, int layout, int wdtype, int variant,
                 cudaStream_t stream);
+
+
+// True when a vectorised NK kernel takes an [n, k] weight of this shape (alignment of
+// freshly allocated device buffers assumed).
+bool nk_fast_eligible(int64_t k, int64_t n, int wdtype);
+
+// dst[cols][rows] = src[rows][cols] for 2- or 4-byte elements, on `stream`.
+int launch_transpose(const void *src, void *dst, int64_t rows, int64_t cols, int elem_bytes, cudaStream_t stream);
 
 }  // namespace dmc

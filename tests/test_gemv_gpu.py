@@ -347,6 +347,65 @@ def test_every_kernel_variant(layout, wdtype):
     lib.dmc_cuda_set_param(b"kn_ksplit", 0)
 
 
+@pytest.mark.parametrize("wdtype", [backend.W_BF16, backend.W_F32])
+@pytest.mark.parametrize("k,n", [(2048, 300), (2560, 1000), (4096, 4096), (6144, 777), (8192, 148), (11008, 512),
+                                 (14336, 301), (16384, 64), (28672, 100), (4096, 1), (4096, 147), (2048 + 8, 149)])
+def test_tma_ring_kernel(k, n, wdtype):
+    """The bulk-copy ring kernel across its register-slice widths, both consumer-warp
+    counts, ragged row counts (fewer rows than CTAs, partial last stage) and ring shapes."""
+    lib = dmc.load()
+    if wdtype == backend.W_F32 and k > 16384:
+        pytest.skip("f32 rows this long go to the LDG kernel")
+    rng = np.random.default_rng(k * 31 + n + wdtype)
+    x = synth.activations(rng, (1, k))
+    if wdtype == backend.W_BF16:
+        w = synth.bf16_weights(rng, (n, k))
+        ref = oracle.gemm_bf16_fma(x, np.ascontiguousarray(w.T))
+        tol = TOL_BF16
+    else:
+        w = synth.f32_weights(rng, (n, k))
+        ref = oracle.gemm_f32_fma(x, np.ascontiguousarray(w.T))
+        tol = TOL_F32
+    dW, dx, dy = backend.DeviceBuffer.from_host(w), backend.DeviceBuffer.from_host(x), backend.DeviceBuffer(n * 4)
+    total = lib.dmc_cuda_variant_count(backend.LAYOUT_NK, wdtype)
+    try:
+        for variant in (total - 2, total - 1):                   # nk_tma_cw8, nk_tma_cw16
+            for ring, stage in ((0, 0), (64, 8), (192, 64), (128, 16)):
+                lib.dmc_cuda_set_param(b"tma_ring_kb", ring)
+                lib.dmc_cuda_set_param(b"tma_stage_kb", stage)
+                lib.dmc_cuda_memset(dy.ptr, 0xFF, n * 4)
+                backend.gemv_dev(dW, dx, dy, 1, k, n, backend.LAYOUT_NK, wdtype, variant)
+                backend.sync()
+                name = lib.dmc_cuda_variant_name(backend.LAYOUT_NK, wdtype, variant).decode()
+                assert_parity(dy.download(F, n), ref, tol, f"{name} ring={ring} stage={stage}")
+    finally:
+        lib.dmc_cuda_set_param(b"tma_ring_kb", 0)
+        lib.dmc_cuda_set_param(b"tma_stage_kb", 0)
+
+
+def test_resident_kn_weight_is_stored_k_contiguous_once():
+    # a [k, n] weight the ring kernel can take is transposed on the device at upload; later calls reuse it
+    lib = dmc.load()
+    lib.dmc_cuda_drop_resident()
+    k, n = 4096, 1024
+    rng = np.random.default_rng(31)
+    w = synth.bf16_weights(rng, (k, n))
+    x = synth.activations(rng, (1, k))
+    ref = oracle.gemm_bf16_fma(x, w)
+    first = lib.dmc_cuda_launch_count()
+    assert_parity(gpu_bf16(x, w, 1, k, n), ref, TOL_BF16)
+    after_first = lib.dmc_cuda_launch_count()
+    assert_parity(gpu_bf16(x, w.copy(), 1, k, n), ref, TOL_BF16)
+    assert after_first - first == 2, "upload = one transpose kernel + one GEMV"
+    assert lib.dmc_cuda_launch_count() - after_first == 1, "second call = one GEMV, no re-upload"
+    assert lib.dmc_cuda_resident_count() == 1
+    # the same bytes viewed with another shape are a different resident entry
+    assert_parity(gpu_bf16(x[:, :2048], w.reshape(2048, 2048), 1, 2048, 2048),
+                  oracle.gemm_bf16_fma(x[:, :2048], w.reshape(2048, 2048)), TOL_BF16)
+    assert lib.dmc_cuda_resident_count() == 2
+    lib.dmc_cuda_drop_resident()
+
+
 def test_lowering_plan_runs_through_the_abi():
     # the whole compile-time decision + runtime call, as the JIT would make it, vs the interpreter's batched `@`
     low = lowering.Lowering(cuda=True)
