@@ -60,6 +60,8 @@ static FpKey fingerprint(const uint8_t *ptr, size_t bytes) {
     return FpKey{h1, h2, (uint64_t)bytes};
 }
 
+void apply_env_params();
+
 static int init_locked(int device) {
     Context &c = g_ctx;
     if (c.ready) return DMC_CUDA_OK;
@@ -85,6 +87,7 @@ static int init_locked(int device) {
     DMC_CUDA_TRY(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
     DMC_CUDA_TRY(cudaMallocHost((void **)&c.err_word, sizeof(int)));
     *c.err_word = 0;
+    apply_env_params();
     c.ready = true;
     return DMC_CUDA_OK;
 }
@@ -201,7 +204,10 @@ static int resident_weight(uintptr_t r, size_t bytes, int64_t k, int64_t n, int 
             return fail(DMC_CUDA_ERR_OOM, "weight upload: staging allocation failed: %s", cudaGetErrorString(e));
         }
     }
-    cudaError_t e = cudaMemcpy(staging, (const void *)r, bytes, cudaMemcpyHostToDevice);
+    // On the context's stream, not the legacy default stream: a plain cudaMemcpy from pageable memory
+    // may return before its DMA lands, and the non-blocking stream would not wait for it.
+    cudaError_t e = cudaMemcpyAsync(staging, (const void *)r, bytes, cudaMemcpyHostToDevice, c.stream);
+    if (e == cudaSuccess && !transposed) e = cudaStreamSynchronize(c.stream);
     if (e == cudaSuccess && transposed) {
         int rc = launch_transpose(staging, d, k, n, (int)wsz, c.stream);
         e = rc ? cudaErrorUnknown : cudaStreamSynchronize(c.stream);  // the GEMV may prefetch W before its dependency wait
@@ -433,7 +439,8 @@ extern "C" int dmc_cuda_register_weight(int64_t ptr, int64_t bytes, int wdtype) 
             return fail(DMC_CUDA_ERR_BAD_ARG, "register_weight: range overlaps a registered range");
     void *d = nullptr;
     DMC_CUDA_TRY(cudaMalloc(&d, (size_t)bytes));
-    cudaError_t e = cudaMemcpy(d, (const void *)ptr, (size_t)bytes, cudaMemcpyHostToDevice);
+    cudaError_t e = cudaMemcpyAsync(d, (const void *)ptr, (size_t)bytes, cudaMemcpyHostToDevice, c.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c.stream);
     if (e != cudaSuccess) {
         cudaFree(d);
         return fail(DMC_CUDA_ERR_CUDA, "register_weight: upload failed: %s", cudaGetErrorString(e));
@@ -476,8 +483,8 @@ extern "C" void dmc_cuda_drop_resident(void) {
     for (const RegisteredRange &rg : c.registered) c.resident_bytes += (int64_t)rg.bytes;
 }
 
-extern "C" int dmc_cuda_set_param(const char *name, int64_t value) {
-    std::lock_guard<std::mutex> lock(ctx_mutex());
+namespace dmc {
+static int apply_param(const char *name, int64_t value) {
     Tuning &t = tuning();
     if (!strcmp(name, "pdl")) t.pdl = (int)value;
     else if (!strcmp(name, "kn_ctas_per_sm")) t.kn_ctas_per_sm = (int)value;
@@ -490,6 +497,29 @@ extern "C" int dmc_cuda_set_param(const char *name, int64_t value) {
     else if (!strcmp(name, "nk_default")) t.nk_default = (int)value;
     else return DMC_CUDA_ERR_BAD_ARG;
     return DMC_CUDA_OK;
+}
+
+// DMC_CUDA_PARAMS="name=value,name=value": the same knobs as dmc_cuda_set_param, read once at
+// context creation (env-var style of the reference's DMC_GPU_PARTS, compiler/src/gpu.rs:552).
+void apply_env_params() {
+    const char *env = getenv("DMC_CUDA_PARAMS");
+    if (!env) return;
+    std::string str(env);
+    size_t pos = 0;
+    while (pos < str.size()) {
+        size_t end = str.find(',', pos);
+        if (end == std::string::npos) end = str.size();
+        std::string kv = str.substr(pos, end - pos);
+        size_t eq = kv.find('=');
+        if (eq != std::string::npos) apply_param(kv.substr(0, eq).c_str(), atoll(kv.c_str() + eq + 1));
+        pos = end + 1;
+    }
+}
+}  // namespace dmc
+
+extern "C" int dmc_cuda_set_param(const char *name, int64_t value) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    return apply_param(name, value);
 }
 
 // ---- device-resident path -----------------------------------------------------------------
