@@ -41,6 +41,7 @@ SIGNATURES = {
     "dmc_cuda_memset": (C.c_int, [VP, C.c_int, I64]),
     "dmc_cuda_sync": (C.c_int, []),
     "dmc_cuda_gemv_dev": (C.c_int, [VP, VP, VP, I64, I64, I64, C.c_int, C.c_int, C.c_int]),
+    "dmc_cuda_gemv_bf16_noalloc": (C.c_int, [VP, VP, VP, I64, I64, VP]),
     "dmc_cuda_bench_items": (C.c_double, [VP, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_variant_count": (C.c_int, [C.c_int, C.c_int]),
     "dmc_cuda_variant_name": (C.c_char_p, [C.c_int, C.c_int, C.c_int]),

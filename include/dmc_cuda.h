@@ -150,6 +150,26 @@ int dmc_cuda_sync(void);
 int dmc_cuda_gemv_dev(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
                       int layout, int wdtype, int variant);
 
+/* y[n] (f32) = x[k] (f32) @ W[k][n] (bf16 bits), all three on the current device, launched on
+ * `stream` (a cudaStream_t, NULL for the default stream) -- without allocating anything.
+ * (No counterpart in the reference: its Metal backend creates buffers freely.)
+ *
+ * For hosts that cannot let a library allocate on their behalf: a runtime that has given the whole
+ * device to its own arena under a hard byte budget, or a decode loop that cannot take the
+ * device-wide stall an allocation or free causes while other streams are running.  This call makes
+ * no cudaMalloc, cudaMallocHost, cudaFree or other allocating call and does not create the
+ * library context; the split-K partial sums go to a fixed ~4 MiB array inside the library image,
+ * which every GPU that loads the library holds until the process exits.
+ *
+ * Limits: n <= 16384 and n % 8 == 0, W 16-byte aligned, k < 2^31; anything else is refused with
+ * DMC_CUDA_ERR_UNSUPPORTED (sticky status and message as for every entry point) and nothing runs.
+ * The first call on each device looks up the array's device address; make that call outside any
+ * stream capture.  All calls share the one array and it keeps the previous call's contents (the
+ * call re-zeroes the arrival counters it needs, on `stream`, before the kernel): two calls whose
+ * kernels can overlap on the GPU -- different streams, or different host threads on one device --
+ * race on it, so keep them ordered on one stream.  Returns a status code. */
+int dmc_cuda_gemv_bf16_noalloc(const void *dW, const float *dx, float *dy, int64_t k, int64_t n, void *stream);
+
 /* One device-resident GEMV of a benchmark step (arguments of dmc_cuda_gemv_dev). */
 typedef struct dmc_gemv_item {
     const void *W;
