@@ -42,6 +42,13 @@ SIGNATURES = {
     "dmc_cuda_sync": (C.c_int, []),
     "dmc_cuda_gemv_dev": (C.c_int, [VP, VP, VP, I64, I64, I64, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_gemv_bf16_noalloc": (C.c_int, [VP, VP, VP, I64, I64, VP]),
+    "dmc_cuda_shard_range": (None, [I64, C.c_int, C.c_int, C.POINTER(I64), C.POINTER(I64)]),
+    "dmc_cuda_shard_unique_id": (C.c_int, [VP]),
+    "dmc_cuda_shard_init": (C.c_int, [C.c_int, C.c_int, VP, I64]),
+    "dmc_cuda_shard_shutdown": (None, []),
+    "dmc_cuda_shard_gemv": (C.c_int, [VP, VP, I64, I64, C.c_int]),
+    "dmc_cuda_shard_output": (VP, []),
+    "dmc_cuda_bench_shard": (C.c_double, [VP, C.c_int, VP, I64, I64, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_bench_items": (C.c_double, [VP, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_variant_count": (C.c_int, [C.c_int, C.c_int]),
     "dmc_cuda_variant_name": (C.c_char_p, [C.c_int, C.c_int, C.c_int]),

@@ -1,0 +1,248 @@
+// shard.cu -- row-sharded GEMV across the GPUs of one box, one process per GPU.
+//
+// y = W.x with W[n][k] split by rows: rank r of `world` owns rows
+// [n*r/world, n*(r+1)/world) -- a contiguous block uploaded once to its own HBM --
+// runs the single-GPU kernel on it, and the f32 output slices are exchanged so every
+// rank ends with the whole y.  The reference has no multi-GPU code at all
+// (collectives are reserved words that error, compiler/src/interp.rs:7431-7446);
+// this is the one exchange the path needs.  K is never split across ranks: that
+// would need a reduction of partial sums (more bytes, a second rounding order).
+//
+// Exchange mode 0: ncclAllGather (ragged splits: one ncclBroadcast per rank in a
+// group) on the context's stream.  NCCL is opened with dlopen so the library loads
+// on hosts without it; an already-loaded copy (e.g. the one PyTorch bundles) is
+// reused rather than loading a second one beside it.
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "runtime.h"
+
+namespace dmc {
+namespace {
+
+typedef struct ncclComm *ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+enum { ncclSuccess = 0, ncclFloat32 = 7, ncclUint8 = 1 };
+
+struct NcclApi {
+    void *lib = nullptr;
+    int (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    int (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    int (*CommDestroy)(ncclComm_t) = nullptr;
+    int (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*Broadcast)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
+    const char *(*GetErrorString)(int) = nullptr;
+};
+
+struct Shard {
+    bool ready = false;
+    int rank = 0, world = 1;
+    ncclComm_t comm = nullptr;
+    float *y = nullptr;  // replicated output, max_n floats
+    int64_t max_n = 0;
+};
+
+NcclApi g_nccl;
+Shard g_shard;
+
+int load_nccl() {
+    if (g_nccl.lib) return DMC_CUDA_OK;
+    void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);  // reuse a copy the process already has
+    if (!h) {
+        const char *env = getenv("DMC_NCCL_LIB");
+        if (env) h = dlopen(env, RTLD_NOW | RTLD_LOCAL);
+    }
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
+    if (!h) return fail(DMC_CUDA_ERR_NCCL, "NCCL is not available: %s", dlerror());
+#define SYM(field, name)                                                                          \
+    *(void **)(&g_nccl.field) = dlsym(h, name);                                                   \
+    if (!g_nccl.field) return fail(DMC_CUDA_ERR_NCCL, "NCCL symbol %s is missing", name);
+    SYM(GetUniqueId, "ncclGetUniqueId")
+    SYM(CommInitRank, "ncclCommInitRank")
+    SYM(CommDestroy, "ncclCommDestroy")
+    SYM(AllGather, "ncclAllGather")
+    SYM(Broadcast, "ncclBroadcast")
+    SYM(GroupStart, "ncclGroupStart")
+    SYM(GroupEnd, "ncclGroupEnd")
+    SYM(GetErrorString, "ncclGetErrorString")
+#undef SYM
+    g_nccl.lib = h;
+    return DMC_CUDA_OK;
+}
+
+#define DMC_NCCL_TRY(expr)                                                                        \
+    do {                                                                                          \
+        int r__ = (expr);                                                                         \
+        if (r__ != ncclSuccess)                                                                   \
+            return fail(DMC_CUDA_ERR_NCCL, "%s failed: %s", #expr, g_nccl.GetErrorString(r__));  \
+    } while (0)
+
+void shard_range(int64_t n, int rank, int world, int64_t *r0, int64_t *r1) {
+    *r0 = n * rank / world;
+    *r1 = n * (rank + 1) / world;
+}
+
+// Local GEMV into y[r0, r1) then the exchange, all on `s`.
+int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype, cudaStream_t s) {
+    Shard &sh = g_shard;
+    if (!sh.ready) return fail(DMC_CUDA_ERR_BAD_ARG, "shard_gemv: dmc_cuda_shard_init has not been called");
+    if (n > sh.max_n) return fail(DMC_CUDA_ERR_UNSUPPORTED, "shard_gemv: n=%lld beyond the max_n=%lld given to shard_init",
+                                  (long long)n, (long long)sh.max_n);
+    int64_t r0, r1;
+    shard_range(n, sh.rank, sh.world, &r0, &r1);
+    int rc = launch_gemv(dW_shard, dx, sh.y + r0, 1, k, r1 - r0, 1, 0, 0, DMC_LAYOUT_NK, wdtype, -1, s);
+    if (rc) return rc;
+    if (sh.world == 1) return DMC_CUDA_OK;
+    if (n % sh.world == 0) {
+        DMC_NCCL_TRY(g_nccl.AllGather(sh.y + r0, sh.y, (size_t)(n / sh.world), ncclFloat32, sh.comm, s));
+    } else {  // ragged: every rank broadcasts its slice
+        DMC_NCCL_TRY(g_nccl.GroupStart());
+        for (int r = 0; r < sh.world; ++r) {
+            int64_t a, b;
+            shard_range(n, r, sh.world, &a, &b);
+            if (b > a) {
+                int e = g_nccl.Broadcast(sh.y + a, sh.y + a, (size_t)(b - a), ncclFloat32, r, sh.comm, s);
+                if (e != ncclSuccess) {
+                    g_nccl.GroupEnd();
+                    return fail(DMC_CUDA_ERR_NCCL, "ncclBroadcast failed: %s", g_nccl.GetErrorString(e));
+                }
+            }
+        }
+        DMC_NCCL_TRY(g_nccl.GroupEnd());
+    }
+    return DMC_CUDA_OK;
+}
+
+}  // namespace
+}  // namespace dmc
+
+using namespace dmc;
+
+extern "C" void dmc_cuda_shard_range(int64_t n, int rank, int world, int64_t *r0, int64_t *r1) {
+    if (world < 1) world = 1;
+    shard_range(n, rank, world, r0, r1);
+}
+
+extern "C" int dmc_cuda_shard_unique_id(uint8_t *out128) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return dmc::status();
+    int rc = load_nccl();
+    if (rc) return rc;
+    ncclUniqueId id;
+    DMC_NCCL_TRY(g_nccl.GetUniqueId(&id));
+    memcpy(out128, id.internal, 128);
+    return DMC_CUDA_OK;
+}
+
+extern "C" int dmc_cuda_shard_init(int rank, int world, const uint8_t *id128, int64_t max_n) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return dmc::status();
+    if (world < 1 || rank < 0 || rank >= world || max_n < 1)
+        return fail(DMC_CUDA_ERR_BAD_ARG, "shard_init: bad rank %d / world %d / max_n %lld", rank, world, (long long)max_n);
+    int rc = ensure_init();
+    if (rc) return rc;
+    Shard &sh = g_shard;
+    if (sh.ready) return fail(DMC_CUDA_ERR_BAD_ARG, "shard_init: already initialised");
+    if (world > 1) {
+        if (!id128) return fail(DMC_CUDA_ERR_BAD_ARG, "shard_init: world > 1 needs the 128-byte NCCL id");
+        rc = load_nccl();
+        if (rc) return rc;
+        ncclUniqueId id;
+        memcpy(id.internal, id128, 128);
+        DMC_NCCL_TRY(g_nccl.CommInitRank(&sh.comm, world, id, rank));
+    }
+    DMC_CUDA_TRY(cudaMalloc((void **)&sh.y, (size_t)max_n * sizeof(float)));
+    DMC_CUDA_TRY(cudaMemset(sh.y, 0, (size_t)max_n * sizeof(float)));
+    sh.rank = rank;
+    sh.world = world;
+    sh.max_n = max_n;
+    sh.ready = true;
+    return DMC_CUDA_OK;
+}
+
+extern "C" void dmc_cuda_shard_shutdown(void) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    Shard &sh = g_shard;
+    if (!sh.ready) return;
+    if (ctx().ready) cudaStreamSynchronize(ctx().stream);
+    if (sh.comm) g_nccl.CommDestroy(sh.comm);
+    if (sh.y) cudaFree(sh.y);
+    sh = Shard();
+}
+
+extern "C" float *dmc_cuda_shard_output(void) { return g_shard.y; }
+
+extern "C" int dmc_cuda_shard_gemv(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return dmc::status();
+    return shard_gemv_on(dW_shard, dx, k, n, wdtype, ctx().stream);
+}
+
+extern "C" double dmc_cuda_bench_shard(const void *const *dW_shards, int copies, const float *dx, int64_t k,
+                                       int64_t n, int wdtype, int steps, int warmup, int use_graph) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return -1.0;
+    if (!g_shard.ready || copies < 1 || steps < 1 || warmup < 0) {
+        fail(DMC_CUDA_ERR_BAD_ARG, "bench_shard: needs shard_init, copies >= 1, steps >= 1");
+        return -1.0;
+    }
+    Context &c = ctx();
+    cudaStream_t s = c.stream;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    double us = -1.0;
+    auto one_step = [&]() -> int {
+        for (int i = 0; i < copies; ++i) {
+            int rc = shard_gemv_on(dW_shards[i], dx, k, n, wdtype, s);
+            if (rc) return rc;
+        }
+        return DMC_CUDA_OK;
+    };
+    auto body = [&]() -> int {
+        int rc = one_step();  // eager: sizes scratch, lets NCCL set up its channels
+        if (rc) return rc;
+        DMC_CUDA_TRY(cudaStreamSynchronize(s));
+        DMC_CUDA_TRY(cudaEventCreate(&e0));
+        DMC_CUDA_TRY(cudaEventCreate(&e1));
+        int64_t per_step = 0;
+        if (use_graph) {
+            const int64_t before = c.launches;
+            DMC_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+            rc = one_step();
+            cudaError_t ce = cudaStreamEndCapture(s, &graph);
+            if (rc) return rc;
+            DMC_CUDA_TRY(ce);
+            per_step = c.launches - before;
+            DMC_CUDA_TRY(cudaGraphInstantiate(&exec, graph, 0));
+        }
+        auto run_step = [&]() -> int {
+            if (!use_graph) return one_step();
+            DMC_CUDA_TRY(cudaGraphLaunch(exec, s));
+            c.launches += per_step;
+            return DMC_CUDA_OK;
+        };
+        for (int i = 0; i < warmup; ++i)
+            if ((rc = run_step())) return rc;
+        DMC_CUDA_TRY(cudaStreamSynchronize(s));
+        DMC_CUDA_TRY(cudaEventRecord(e0, s));
+        for (int i = 0; i < steps; ++i)
+            if ((rc = run_step())) return rc;
+        DMC_CUDA_TRY(cudaEventRecord(e1, s));
+        DMC_CUDA_TRY(cudaStreamSynchronize(s));
+        float ms = 0.0f;
+        DMC_CUDA_TRY(cudaEventElapsedTime(&ms, e0, e1));
+        us = (double)ms * 1000.0 / steps;
+        return DMC_CUDA_OK;
+    };
+    body();
+    if (exec) cudaGraphExecDestroy(exec);
+    if (graph) cudaGraphDestroy(graph);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    return dmc::status() ? -1.0 : us;
+}

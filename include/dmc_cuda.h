@@ -187,6 +187,34 @@ typedef struct dmc_gemv_item {
  * replayed.  Returns microseconds per step (< 0 on error). */
 double dmc_cuda_bench_items(const dmc_gemv_item *items, int count, int steps, int warmup, int use_graph);
 
+/* ---- row-sharded GEMV over the GPUs of one box (one process per GPU) ------------------------
+ * No counterpart in the reference, which has no multi-GPU code (its collective names are reserved
+ * words that error at run time, compiler/src/interp.rs:7431-7446). */
+
+/* Rows [*r0, *r1) of an n-row weight that `rank` of `world` owns: n*rank/world .. n*(rank+1)/world.
+ * Pure; no device. */
+void dmc_cuda_shard_range(int64_t n, int rank, int world, int64_t *r0, int64_t *r1);
+
+/* Rank 0 creates the 128-byte NCCL id and hands it to the other ranks by any host channel. */
+int dmc_cuda_shard_unique_id(uint8_t *out128);
+
+/* Join the communicator (collective: every rank calls it) and allocate the replicated output of
+ * up to `max_n` floats.  world == 1 needs no id and no NCCL. */
+int dmc_cuda_shard_init(int rank, int world, const uint8_t *id128, int64_t max_n);
+void dmc_cuda_shard_shutdown(void);
+
+/* y = W.x for W[n][k] (k contiguous) of which this rank holds rows dmc_cuda_shard_range(n, rank, world)
+ * in `dW_shard` (device).  Runs the local GEMV, then all-gathers the f32 slices so every rank holds
+ * the whole y in dmc_cuda_shard_output().  Asynchronous on the context's stream; collective. */
+int dmc_cuda_shard_gemv(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype);
+float *dmc_cuda_shard_output(void);
+
+/* Device-timed benchmark of the call above on this rank: a step is one sharded GEMV per entry of
+ * dW_shards (distinct copies of the shard, so the step's working set exceeds L2).  Returns this
+ * rank's microseconds per step; the caller takes the maximum over ranks.  Collective. */
+double dmc_cuda_bench_shard(const void *const *dW_shards, int copies, const float *dx, int64_t k, int64_t n,
+                            int wdtype, int steps, int warmup, int use_graph);
+
 /* Number of kernel configurations a layout/type offers, and a printable name. */
 int dmc_cuda_variant_count(int layout, int wdtype);
 const char *dmc_cuda_variant_name(int layout, int wdtype, int variant);
