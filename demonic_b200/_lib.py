@@ -49,6 +49,7 @@ SIGNATURES = {
     "dmc_cuda_shard_gemv": (C.c_int, [VP, VP, I64, I64, C.c_int]),
     "dmc_cuda_shard_output": (VP, []),
     "dmc_cuda_bench_shard": (C.c_double, [VP, C.c_int, VP, I64, I64, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "dmc_cuda_gemm_dev": (C.c_int, [VP, VP, VP, I64, I64, I64, C.c_int]),
     "dmc_cuda_bench_items": (C.c_double, [VP, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_variant_count": (C.c_int, [C.c_int, C.c_int]),
     "dmc_cuda_variant_name": (C.c_char_p, [C.c_int, C.c_int, C.c_int]),

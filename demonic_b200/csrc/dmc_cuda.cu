@@ -370,6 +370,7 @@ extern "C" void dmc_cuda_shutdown(void) {
     if (c.partial) cudaFree(c.partial);
     if (c.counters) cudaFree(c.counters);
     if (c.d_tmpw) cudaFree(c.d_tmpw);
+    if (c.d_tmpx) cudaFree(c.d_tmpx);
     if (c.err_word) cudaFreeHost(c.err_word);
     cudaStreamDestroy(c.stream);
     c = Context();
@@ -495,6 +496,11 @@ static int apply_param(const char *name, int64_t value) {
     else if (!strcmp(name, "tma_ctas_per_sm")) t.tma_ctas_per_sm = (int)value;
     else if (!strcmp(name, "store_nk")) t.store_nk = (int)value;
     else if (!strcmp(name, "nk_default")) t.nk_default = (int)value;
+    else if (!strcmp(name, "shard_fused")) t.shard_fused = (int)value;
+    else if (!strcmp(name, "shard_debug")) t.shard_debug = (int)value;
+    else if (!strcmp(name, "tc_ksplit")) t.tc_ksplit = (int)value;
+    else if (!strcmp(name, "tc_smem_kb")) t.tc_smem_kb = (int)value;
+    else if (!strcmp(name, "tc_min_m")) t.tc_min_m = (int)value;
     else return DMC_CUDA_ERR_BAD_ARG;
     return DMC_CUDA_OK;
 }
@@ -572,6 +578,25 @@ extern "C" int dmc_cuda_gemv_dev(const void *dW, const float *dx, float *dy, int
     int rc = ensure_init();
     if (rc) return rc;
     return launch_gemv(dW, dx, dy, m, k, n, 1, 0, 0, layout, wdtype, variant, ctx().stream);
+}
+
+extern "C" int dmc_cuda_gemm_dev(const void *dW, const void *dX, float *dY, int64_t m, int64_t k, int64_t n,
+                                 int xdtype) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return dmc::status();
+    int rc = ensure_init();
+    if (rc) return rc;
+    if (m <= 0 || n <= 0) return DMC_CUDA_OK;
+    if (k == 0) {
+        DMC_CUDA_TRY(cudaMemsetAsync(dY, 0, (size_t)m * n * sizeof(float), ctx().stream));
+        return DMC_CUDA_OK;
+    }
+    if (!gemm_tc_eligible(m, k, n, dW, dX))
+        return fail(DMC_CUDA_ERR_UNSUPPORTED, "gemm: needs k %% 8 == 0 and 16-byte aligned operands (m=%lld k=%lld n=%lld)",
+                    (long long)m, (long long)k, (long long)n);
+    if (xdtype == DMC_X_BF16) return launch_gemm_tc(dW, dX, dY, m, k, n, 0, ctx().stream);
+    if (xdtype == DMC_X_F32) return launch_gemm_tc_f32x(dW, (const float *)dX, dY, m, k, n, ctx().stream);
+    return fail(DMC_CUDA_ERR_BAD_ARG, "gemm: unknown activation type %d", xdtype);
 }
 
 extern "C" double dmc_cuda_bench_items(const dmc_gemv_item *items, int count, int steps, int warmup,

@@ -17,6 +17,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "peer.cuh"
+
 namespace dmc {
 
 struct GemvArgs {
@@ -29,6 +31,8 @@ struct GemvArgs {
     int kchunk, ksplit;  // KN: rows of k per CTA along grid.y
     int colblocks;       // KN: CTAs along n per batch slice
     long long ls, rs;    // batch strides in elements (x: f32, W: weight elements)
+    const PeerOut *peer; // NK kernel, sharded path: store y into every rank's replica (else null)
+    long long yoff;      // first row of this rank's slice within the replicated y
 };
 
 // ---- small device helpers ---------------------------------------------------
@@ -325,11 +329,14 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
         }
     };
 
+    __shared__ int s_last;
     int g = blockIdx.x * WARPS + warp;
     const bool any = g * R < N;
     if (any) load_w(g, lane);
     griddep_launch_dependents();
     griddep_wait();
+    // after the wait: the previous exchange (an earlier kernel) is what advances the epoch word
+    const unsigned epoch = a.peer ? peer_epoch(a.peer) : 0u;
 
     // stage x (after the dependency wait: an earlier kernel may produce it)
     {
@@ -362,9 +369,13 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
             const int row = g * R + j;
-            if (lane == 0 && row < N) a.y[row] = s;
+            if (lane == 0 && row < N) {
+                if (a.peer) peer_store(a.peer, epoch, a.yoff + row, s);
+                else a.y[row] = s;
+            }
         }
     }
+    if (a.peer) peer_finish<THREADS>(a.peer, epoch, a.yoff, N, &s_last);
 }
 
 // Any-shape NK fallback: one warp per row, scalar loads.

@@ -65,6 +65,8 @@ static const NkVariant kNk[] = {
 };
 constexpr int kNkCount = sizeof(kNk) / sizeof(kNk[0]);
 
+}  // namespace
+
 int launch_ex(const void *fn, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, void **params) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -109,6 +111,8 @@ int ensure_scratch(size_t partial_bytes, size_t ncounters) {
     }
     return DMC_CUDA_OK;
 }
+
+namespace {
 
 // Default configuration per shape (from the B200 sweeps; see profiles/).
 int default_kn_variant(int64_t k, int64_t n) {
@@ -283,6 +287,11 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
     const size_t smem = (size_t)((k + 255) / 256 * 256) * sizeof(float);
     const bool vec_ok = k % epv == 0 && ((uintptr_t)dW % 16) == 0 && ((uintptr_t)dx % 16) == 0 &&
                         smem <= 200 * 1024;
+    if (c.peer) {  // fused exchange lives in the vectorised LDG kernel only
+        if (!vec_ok || m != 1)
+            return fail(DMC_CUDA_ERR_UNSUPPORTED, "sharded gemv: needs m == 1, k %% %d == 0 and aligned buffers", epv);
+        if (variant < 0 || variant >= kNkCount) variant = default_nk_variant(k, n);
+    }
     if (variant < 0 && tuning().nk_default >= 0) variant = tuning().nk_default;
     if (variant == kTmaVariantCw8 || variant == kTmaVariantCw16) {
         TmaPlan p = plan_tma(k, n, wdtype, variant == kTmaVariantCw8 ? 8 : 16, dW, dx);
@@ -318,6 +327,8 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
     if (tuning().nk_ctas_per_sm > 0) cps = std::min(cps, tuning().nk_ctas_per_sm);
     const int64_t groups = (n + (int64_t)v.WARPS * v.R - 1) / ((int64_t)v.WARPS * v.R);
     const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(groups, (int64_t)c.sm_count * cps));
+    a.peer = static_cast<const PeerOut *>(c.peer);
+    a.yoff = c.peer_yoff;
     for (int64_t mi = 0; mi < m; ++mi) {
         a.x = dx + mi * k;
         a.y = dy + mi * n;

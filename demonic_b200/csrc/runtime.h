@@ -60,6 +60,9 @@ struct Context {
     // transient f32 operand upload buffer (dmc_matmul_f32_gpu)
     char *d_tmpw = nullptr;
     size_t tmpw_cap = 0;
+    // (hi, lo) bf16 split of f32 activations for the tensor-core GEMM
+    char *d_tmpx = nullptr;
+    size_t tmpx_cap = 0;
 
     // resident weights
     std::unordered_map<FpKey, void *, FpKeyHash> by_fingerprint;
@@ -68,6 +71,10 @@ struct Context {
 
     // error word written by kernels whose bounded waits run out (pinned, device-visible)
     int *err_word = nullptr;
+
+    // set by the sharded path around a launch: the NK kernel then stores y into every rank's replica
+    const void *peer = nullptr;  // device pointer to a PeerOut
+    long long peer_yoff = 0;
 
     int64_t launches = 0;
 };
@@ -83,6 +90,11 @@ struct Tuning {
     int tma_ctas_per_sm = 0;
     int store_nk = 1;       // keep resident [k,n] weights k-contiguous on the device
     int nk_default = -1;    // NK variant used when the caller passes -1 (-1 = library choice)
+    int tc_ksplit = 0;      // tcgen05 GEMM: K splits (0 = derive from the tile count)
+    int tc_smem_kb = 0;     // tcgen05 GEMM: shared-memory ring budget per CTA
+    int tc_min_m = 0;       // activation rows from which `@` goes to the tensor cores (0 = library default)
+    int shard_debug = 0;
+    int shard_fused = 1;    // sharded GEMV: 1 = peer stores fused into the kernel, 0 = NCCL all-gather
 };
 
 Context &ctx();
@@ -108,6 +120,18 @@ int launch_gemv(const void *dW, const float *dx, float *dy, int64_t m, int64_t k
                 int64_t batch, int64_t ls, int64_t rs, int layout, int wdtype, int variant,
                 cudaStream_t stream);
 
+
+// One kernel launch with the library's launch attributes (programmatic dependent launch).
+int launch_ex(const void *fn, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, void **params);
+// Grow the context's split-K scratch (partials in bytes, arrival counters in elements).
+int ensure_scratch(size_t partial_bytes, size_t ncounters);
+
+// tcgen05 GEMM: Y[m][n] = X @ W' with W [n][k] bf16 (k contiguous) and X bf16 or f32.
+bool gemm_tc_eligible(int64_t m, int64_t k, int64_t n, const void *dW, const void *dX);
+int launch_gemm_tc(const void *dW, const void *dXbf16, float *dY, int64_t m, int64_t k, int64_t n, int pair,
+                   cudaStream_t stream);
+int launch_gemm_tc_f32x(const void *dW, const float *dX, float *dY, int64_t m, int64_t k, int64_t n,
+                        cudaStream_t stream);
 
 // True when a vectorised NK kernel takes an [n, k] weight of this shape (alignment of
 // freshly allocated device buffers assumed).

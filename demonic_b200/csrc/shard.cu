@@ -17,6 +17,7 @@
 #include <algorithm>
 #include <cstring>
 
+#include "peer.cuh"
 #include "runtime.h"
 
 namespace dmc {
@@ -42,9 +43,20 @@ struct Shard {
     bool ready = false;
     int rank = 0, world = 1;
     ncclComm_t comm = nullptr;
-    float *y = nullptr;  // replicated output, max_n floats
+    // one allocation, shared with the peers through CUDA IPC:
+    //   [2 * max_n floats: y, double-buffered by epoch] [kMaxPeers flag words] [epoch] [CTA counter]
+    char *region = nullptr;
+    float *y = nullptr;
     int64_t max_n = 0;
+    void *peer_base[kMaxPeers] = {};  // peers' regions as mapped here (own entry = region)
+    PeerOut *d_peer = nullptr;        // device copy of the exchange descriptor
+    unsigned *d_epoch = nullptr;
+    bool fused_ok = false;            // peer mappings are in place
+    bool last_fused = false;          // which buffer holds the latest result
 };
+constexpr size_t kTailBytes = 256;
+
+size_t region_bytes(int64_t max_n) { return (size_t)2 * max_n * sizeof(float) + kTailBytes; }
 
 NcclApi g_nccl;
 Shard g_shard;
@@ -94,6 +106,18 @@ int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, i
                                   (long long)n, (long long)sh.max_n);
     int64_t r0, r1;
     shard_range(n, sh.rank, sh.world, &r0, &r1);
+    if (tuning().shard_fused && sh.fused_ok && r1 > r0 && k > 0) {
+        // one kernel: GEMV whose epilogue stores into every replica and closes with the flag exchange
+        Context &c = ctx();
+        c.peer = sh.d_peer;
+        c.peer_yoff = r0;
+        int rc = launch_gemv(dW_shard, dx, sh.y + r0, 1, k, r1 - r0, 1, 0, 0, DMC_LAYOUT_NK, wdtype, -1, s);
+        c.peer = nullptr;
+        c.peer_yoff = 0;
+        sh.last_fused = true;
+        return rc;
+    }
+    sh.last_fused = false;
     int rc = launch_gemv(dW_shard, dx, sh.y + r0, 1, k, r1 - r0, 1, 0, 0, DMC_LAYOUT_NK, wdtype, -1, s);
     if (rc) return rc;
     if (sh.world == 1) return DMC_CUDA_OK;
@@ -155,11 +179,61 @@ extern "C" int dmc_cuda_shard_init(int rank, int world, const uint8_t *id128, in
         memcpy(id.internal, id128, 128);
         DMC_NCCL_TRY(g_nccl.CommInitRank(&sh.comm, world, id, rank));
     }
-    DMC_CUDA_TRY(cudaMalloc((void **)&sh.y, (size_t)max_n * sizeof(float)));
-    DMC_CUDA_TRY(cudaMemset(sh.y, 0, (size_t)max_n * sizeof(float)));
+    const size_t bytes = region_bytes(max_n);
+    DMC_CUDA_TRY(cudaMalloc((void **)&sh.region, bytes));
+    DMC_CUDA_TRY(cudaMemset(sh.region, 0, bytes));
+    sh.y = reinterpret_cast<float *>(sh.region);
+    sh.max_n = max_n;
     sh.rank = rank;
     sh.world = world;
-    sh.max_n = max_n;
+    sh.peer_base[rank] = sh.region;
+    sh.fused_ok = world <= kMaxPeers;
+    if (world > 1 && sh.fused_ok) {
+        // exchange the IPC handle of the region through the communicator itself
+        cudaIpcMemHandle_t mine, all[kMaxPeers];
+        DMC_CUDA_TRY(cudaIpcGetMemHandle(&mine, sh.region));
+        char *d_h = nullptr;
+        DMC_CUDA_TRY(cudaMalloc((void **)&d_h, sizeof(mine) * world));
+        DMC_CUDA_TRY(cudaMemcpy(d_h + sizeof(mine) * rank, &mine, sizeof(mine), cudaMemcpyHostToDevice));
+        cudaStream_t s = ctx().stream;
+        DMC_NCCL_TRY(g_nccl.AllGather(d_h + sizeof(mine) * rank, d_h, sizeof(mine), ncclUint8, sh.comm, s));
+        DMC_CUDA_TRY(cudaStreamSynchronize(s));
+        DMC_CUDA_TRY(cudaMemcpy(all, d_h, sizeof(mine) * world, cudaMemcpyDeviceToHost));
+        cudaFree(d_h);
+        for (int r = 0; r < world; ++r) {
+            if (r == rank) continue;
+            cudaError_t e = cudaIpcOpenMemHandle(&sh.peer_base[r], all[r], cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) {  // no peer access between these GPUs: keep the NCCL exchange
+                cudaGetLastError();
+                sh.fused_ok = false;
+                break;
+            }
+        }
+    }
+    if (sh.fused_ok) {
+        PeerOut po = {};
+        for (int r = 0; r < world; ++r) {
+            char *base = static_cast<char *>(sh.peer_base[r]);
+            po.y[r] = reinterpret_cast<float *>(base);
+            po.flags[r] = reinterpret_cast<unsigned *>(base + (size_t)2 * max_n * sizeof(float));
+        }
+        unsigned *tail = reinterpret_cast<unsigned *>(sh.region + (size_t)2 * max_n * sizeof(float));
+        po.epoch = tail + kMaxPeers;
+        po.counter = tail + kMaxPeers + 1;
+        po.err = ctx().err_word;
+        po.stride = max_n;
+        po.world = world;
+        po.rank = rank;
+        po.debug = tuning().shard_debug;
+        sh.d_epoch = po.epoch;
+        DMC_CUDA_TRY(cudaMalloc((void **)&sh.d_peer, sizeof(PeerOut)));
+        DMC_CUDA_TRY(cudaMemcpy(sh.d_peer, &po, sizeof(po), cudaMemcpyHostToDevice));
+    }
+    if (world > 1) {  // nobody may store into a peer before that peer has zeroed its flags
+        DMC_NCCL_TRY(g_nccl.AllGather(sh.y + rank, sh.y, 1, ncclFloat32, sh.comm, ctx().stream));
+        DMC_CUDA_TRY(cudaStreamSynchronize(ctx().stream));
+        DMC_CUDA_TRY(cudaMemset(sh.y, 0, (size_t)world * sizeof(float)));
+    }
     sh.ready = true;
     return DMC_CUDA_OK;
 }
@@ -169,12 +243,25 @@ extern "C" void dmc_cuda_shard_shutdown(void) {
     Shard &sh = g_shard;
     if (!sh.ready) return;
     if (ctx().ready) cudaStreamSynchronize(ctx().stream);
+    for (int r = 0; r < sh.world && r < kMaxPeers; ++r)
+        if (r != sh.rank && sh.peer_base[r]) cudaIpcCloseMemHandle(sh.peer_base[r]);
     if (sh.comm) g_nccl.CommDestroy(sh.comm);
-    if (sh.y) cudaFree(sh.y);
+    if (sh.d_peer) cudaFree(sh.d_peer);
+    if (sh.region) cudaFree(sh.region);
     sh = Shard();
 }
 
-extern "C" float *dmc_cuda_shard_output(void) { return g_shard.y; }
+extern "C" float *dmc_cuda_shard_output(void) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    Shard &sh = g_shard;
+    if (!sh.ready) return nullptr;
+    if (!sh.last_fused) return sh.y;
+    // the fused exchange alternates between two buffers; the epoch word says which one is current
+    unsigned e = 0;
+    cudaStreamSynchronize(ctx().stream);
+    cudaMemcpy(&e, sh.d_epoch, sizeof(e), cudaMemcpyDeviceToHost);
+    return sh.y + (size_t)(e & 1u) * sh.max_n;
+}
 
 extern "C" int dmc_cuda_shard_gemv(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype) {
     std::lock_guard<std::mutex> lock(ctx_mutex());

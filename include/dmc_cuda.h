@@ -47,6 +47,9 @@ enum {
 /* Weight element types. */
 enum { DMC_W_BF16 = 0, DMC_W_F32 = 1 };
 
+/* Activation element types of the tensor-core GEMM. */
+enum { DMC_X_BF16 = 0, DMC_X_F32 = 1 };
+
 /* ---- lifecycle and errors ------------------------------------------------- */
 
 /* Number of usable CUDA devices (0 when there is no driver or device).  The
@@ -169,6 +172,13 @@ int dmc_cuda_gemv_dev(const void *dW, const float *dx, float *dy, int64_t m, int
  * kernels can overlap on the GPU -- different streams, or different host threads on one device --
  * race on it, so keep them ordered on one stream.  Returns a status code. */
 int dmc_cuda_gemv_bf16_noalloc(const void *dW, const float *dx, float *dy, int64_t k, int64_t n, void *stream);
+
+/* Y[m][n] (f32) = X[m][k] @ W', W[n][k] bf16 bits (k contiguous), all on the device: the tcgen05 /
+ * TMEM tensor-core GEMM, for `@` sites that are real contractions (several activation rows).  X is
+ * bf16 bits (DMC_X_BF16; an extension -- the reference's left operand is always f32,
+ * compiler/src/jit.rs:14510-14513) or f32 (DMC_X_F32: split on the device into two bf16 terms so the
+ * product sees x to 16 mantissa bits).  Needs k % 8 == 0.  Asynchronous on the context's stream. */
+int dmc_cuda_gemm_dev(const void *dW, const void *dX, float *dY, int64_t m, int64_t k, int64_t n, int xdtype);
 
 /* One device-resident GEMV of a benchmark step (arguments of dmc_cuda_gemv_dev). */
 typedef struct dmc_gemv_item {

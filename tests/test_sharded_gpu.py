@@ -26,11 +26,15 @@ def test_world_of_one_is_the_plain_gemv():
     sharded.init(0, 1, None, n)
     try:
         dW, dx = backend.DeviceBuffer.from_host(w), backend.DeviceBuffer.from_host(x)
-        sharded.gemv(dW, dx, k, n)
-        y = sharded.output(n)
-        assert_parity(y, oracle.gemm_bf16_fma(x.reshape(1, k), np.ascontiguousarray(w.T)), TOL_BF16)
-        us = sharded.bench([dW], dx, k, n, steps=3, warmup=1)
+        ref = oracle.gemm_bf16_fma(x.reshape(1, k), np.ascontiguousarray(w.T))
+        for fused in (1, 0, 1, 1):          # the fused epilogue (a world of one stores only to itself) and the plain path
+            lib.dmc_cuda_set_param(b"shard_fused", fused)
+            sharded.gemv(dW, dx, k, n)
+            assert_parity(sharded.output(n), ref, TOL_BF16, f"fused={fused}")
+        us = sharded.bench([dW], dx, k, n, steps=3, warmup=1)      # graph replays advance the epoch on the device
         assert us > 0
+        sharded.gemv(dW, dx, k, n)
+        assert_parity(sharded.output(n), ref, TOL_BF16, "after graph replays")
     finally:
         sharded.shutdown()
     assert lib.dmc_cuda_status() == 0
@@ -56,11 +60,17 @@ for n in (8192, 1001):                      # even split (all-gather) and ragged
     if n == 8192: sharded.init(rank, world, ids[0], 8192)
     r0, r1 = sharded.shard_range(n, rank, world)
     dW, dx = backend.DeviceBuffer.from_host(w[r0:r1]), backend.DeviceBuffer.from_host(x)
+    ref = synth.bf16_to_f32(w).astype(np.float64) @ x.astype(np.float64)
+    for fused in (1, 1, 0, 1):               # peer-store epilogue (twice: both y buffers), NCCL exchange, fused again
+        lib.dmc_cuda_set_param(b"shard_fused", fused)
+        sharded.gemv(dW, dx, k, n)
+        y = sharded.output(n)
+        err = float(np.max(np.abs(y - ref)) / np.max(np.abs(ref)))
+        assert err < 1e-5, (rank, n, fused, err)
+    us = sharded.bench([dW], dx, k, n, steps=5, warmup=2)
     sharded.gemv(dW, dx, k, n)
     y = sharded.output(n)
-    ref = synth.bf16_to_f32(w).astype(np.float64) @ x.astype(np.float64)
-    err = float(np.max(np.abs(y - ref)) / np.max(np.abs(ref)))
-    assert err < 1e-5, (rank, n, err)
+    assert float(np.max(np.abs(y - ref)) / np.max(np.abs(ref))) < 1e-5, "after graph replays"
     np.save(os.path.join({out!r}, f"y{{rank}}_{{n}}.npy"), y)
 dist.barrier()
 sharded.shutdown()
