@@ -62,7 +62,7 @@ SIGNATURES = {
 class GemvItem(C.Structure):
     """``dmc_gemv_item`` of include/dmc_cuda.h."""
     _fields_ = [("W", VP), ("x", VP), ("y", VP), ("m", I64), ("k", I64), ("n", I64),
-                ("layout", C.c_int), ("wdtype", C.c_int), ("variant", C.c_int)]
+                ("layout", C.c_int), ("wdtype", C.c_int), ("variant", C.c_int), ("op", C.c_int)]
 
 
 _lib = None

@@ -616,7 +616,10 @@ extern "C" double dmc_cuda_bench_items(const dmc_gemv_item *items, int count, in
     auto one_step = [&]() -> int {
         for (int i = 0; i < count; ++i) {
             const dmc_gemv_item &it = items[i];
-            int rc = launch_gemv(it.W, it.x, it.y, it.m, it.k, it.n, 1, 0, 0, it.layout, it.wdtype, it.variant, s);
+            int rc;
+            if (it.op == 1) rc = launch_gemm_tc(it.W, it.x, it.y, it.m, it.k, it.n, 0, s);
+            else if (it.op == 2) rc = launch_gemm_tc_f32x(it.W, it.x, it.y, it.m, it.k, it.n, s);
+            else rc = launch_gemv(it.W, it.x, it.y, it.m, it.k, it.n, 1, 0, 0, it.layout, it.wdtype, it.variant, s);
             if (rc) return rc;
         }
         return DMC_CUDA_OK;

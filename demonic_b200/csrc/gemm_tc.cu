@@ -67,7 +67,7 @@ int launch_gemm_tc(const void *dW, const void *dXbf16, float *dY, int64_t m, int
     int64_t ksplit = 1;
     const int64_t tiles = tiles_n * tiles_m;
     if (tuning().tc_ksplit > 0) ksplit = tuning().tc_ksplit;
-    else if (tiles < 2 * c.sm_count) ksplit = (2 * c.sm_count + tiles - 1) / tiles;
+    else if (tiles < 2 * c.sm_count) ksplit = std::max<int64_t>(1, (2 * c.sm_count) / tiles);  // never more CTAs than two per SM
     ksplit = std::max<int64_t>(1, std::min<int64_t>(ksplit, std::max<int64_t>(1, kblocks / 4)));
     int64_t per = (kblocks + ksplit - 1) / ksplit;
     ksplit = (kblocks + per - 1) / per;

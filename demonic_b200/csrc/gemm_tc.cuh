@@ -76,13 +76,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t tmem_base = tmem_base_s;
 
     griddep_launch_dependents();
-    griddep_wait();  // X may come from the previous kernel in the stream
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < nkb; ++i) {
+            // The weights never depend on an earlier kernel: their first ring-full of tiles is
+            // requested before the programmatic-dependency wait; X (which may) only after it.
+            const int pre = min(S, nkb);
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(&full[i], STAGE);
+                tc::tma_load_2d(smem + (size_t)i * STAGE, &map_w, (kb0 + i) * kTcBK, tile_n * kTcBM, &full[i]);
+            }
+            griddep_wait();
+            for (int i = 0; i < pre; ++i)
+                tc::tma_load_2d(smem + (size_t)i * STAGE + kTcWTileBytes, &map_x, (kb0 + i) * kTcBK, tile_m * NB, &full[i]);
+            for (int i = pre; i < nkb; ++i) {
                 const int s = i % S;
-                if (i >= S && !mbar_wait(&empty[s], ((i / S) - 1) & 1)) {
+                if (!mbar_wait(&empty[s], ((i / S) - 1) & 1)) {
                     *(volatile int *)a.err = 4;
                     abort_s = 1;
                     break;
@@ -122,6 +131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int row = q * 32 + lane;          // accumulator row = W row inside the tile
         const int n = tile_n * kTcBM + row;
         bool ok = nkb > 0;
+        griddep_wait();  // y / the split-K scratch may still be in use by the previous kernel
         if (ok && !mbar_wait(&done, 0)) {
             *(volatile int *)a.err = 6;
             abort_s = 1;
@@ -167,11 +177,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int div = a.pair ? 2 : 1;
             const int m0 = tile_m * NB / div, m1 = min(a.m, (tile_m + 1) * NB / div);
             const int n0 = tile_n * kTcBM, nn = min(kTcBM, a.n - n0);
-            for (int idx = tid; idx < (m1 - m0) * nn; idx += blockDim.x) {
-                const int mj = m0 + idx / nn, n = n0 + idx % nn;
-                float s = 0.0f;
-                for (int j = 0; j < a.ksplit; ++j) s += __ldcg(&a.partial[((size_t)j * a.m + mj) * a.n + n]);
-                a.y[(size_t)mj * a.n + n] = s;
+            const size_t slab = (size_t)a.m * a.n;  // one split's partial matrix
+            if ((a.n & 3) == 0 && (nn & 3) == 0) {
+                // 128-bit loads, eight splits in flight per thread, summed in split order
+                const int nv = nn >> 2;
+                for (int idx = tid; idx < (m1 - m0) * nv; idx += blockDim.x) {
+                    const size_t off = (size_t)(m0 + idx / nv) * a.n + n0 + (size_t)(idx % nv) * 4;
+                    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int j0 = 0; j0 < a.ksplit; j0 += 8) {
+                        float4 v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            v[j] = (j0 + j < a.ksplit)
+                                       ? __ldcg(reinterpret_cast<const float4 *>(a.partial + (size_t)(j0 + j) * slab + off))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            s.x += v[j].x;
+                            s.y += v[j].y;
+                            s.z += v[j].z;
+                            s.w += v[j].w;
+                        }
+                    }
+                    *reinterpret_cast<float4 *>(a.y + off) = s;
+                }
+            } else {
+                for (int idx = tid; idx < (m1 - m0) * nn; idx += blockDim.x) {
+                    const int mj = m0 + idx / nn, n = n0 + idx % nn;
+                    float s = 0.0f;
+                    for (int j = 0; j < a.ksplit; ++j) s += __ldcg(&a.partial[(size_t)j * slab + (size_t)mj * a.n + n]);
+                    a.y[(size_t)mj * a.n + n] = s;
+                }
             }
             if (tid == 0) a.counters[group] = 0u;
         }

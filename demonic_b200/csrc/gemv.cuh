@@ -293,18 +293,25 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
     const int K = a.K, N = a.N;
     const int nvec = K / EPV;
     const uint4 *W4 = reinterpret_cast<const uint4 *>(a.W);
-    const int gstride = gridDim.x * WARPS;
+
+    // Row groups of R rows.  Normally the groups are dealt round-robin over all warps of the grid
+    // (best balance); for the fused exchange a CTA takes one contiguous block of rows instead, so
+    // that it can push its finished rows to the peers as one run.
+    const bool block_rows = a.peer != nullptr;
+    const int rbeg = block_rows ? (int)(((long long)N * blockIdx.x) / gridDim.x) : 0;
+    const int rend = block_rows ? (int)(((long long)N * (blockIdx.x + 1)) / gridDim.x) : N;
+    const int rstride = block_rows ? WARPS * R : (int)gridDim.x * WARPS * R;
 
     uint4 w[R][U];
-    auto load_w = [&](int g, int c) {
+    auto load_w = [&](int row0, int c) {
 #pragma unroll
         for (int j = 0; j < R; ++j) {
-            const int row = g * R + j;
+            const int row = row0 + j;
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int cc = c + 32 * u;
-                w[j][u] = (row < N && cc < nvec) ? ldg_stream16(W4 + (size_t)row * nvec + cc)
-                                                 : make_uint4(0, 0, 0, 0);
+                w[j][u] = (row < rend && cc < nvec) ? ldg_stream16(W4 + (size_t)row * nvec + cc)
+                                                    : make_uint4(0, 0, 0, 0);
             }
         }
     };
@@ -330,9 +337,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
     };
 
     __shared__ int s_last;
-    int g = blockIdx.x * WARPS + warp;
-    const bool any = g * R < N;
-    if (any) load_w(g, lane);
+    int row0 = block_rows ? rbeg + warp * R : ((int)blockIdx.x * WARPS + warp) * R;
+    if (row0 < rend) load_w(row0, lane);
     griddep_launch_dependents();
     griddep_wait();
     // after the wait: the previous exchange (an earlier kernel) is what advances the epoch word
@@ -355,11 +361,11 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
     __syncthreads();
 
     bool first = true;
-    for (; g * R < N; g += gstride) {
+    for (; row0 < rend; row0 += rstride) {
 #pragma unroll
         for (int j = 0; j < R; ++j) acc[j] = 0.0f;
         for (int c = lane; c < nvec; c += 32 * U) {
-            if (!first) load_w(g, c);
+            if (!first) load_w(row0, c);
             first = false;
             consume(c);
         }
@@ -368,14 +374,18 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
             float s = acc[j];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            const int row = g * R + j;
-            if (lane == 0 && row < N) {
+            const int row = row0 + j;
+            if (lane == 0 && row < rend) {
                 if (a.peer) peer_store(a.peer, epoch, a.yoff + row, s);
                 else a.y[row] = s;
             }
         }
     }
-    if (a.peer) peer_finish<THREADS>(a.peer, epoch, a.yoff, N, &s_last);
+    if (a.peer) {
+        __syncthreads();
+        peer_push<THREADS>(a.peer, epoch, a.yoff + rbeg, rend - rbeg);
+    }
+    if (a.peer) peer_finish<THREADS>(a.peer, epoch, &s_last);
 }
 
 // Any-shape NK fallback: one warp per row, scalar loads.

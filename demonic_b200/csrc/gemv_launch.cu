@@ -375,6 +375,12 @@ int launch_gemv(const void *dW, const float *dx, float *dy, int64_t m, int64_t k
     if (layout == DMC_LAYOUT_KN) return launch_kn(dW, dx, dy, m, k, n, batch, ls, rs, wdtype, variant, stream);
     if (layout == DMC_LAYOUT_NK) {
         if (batch != 1) return fail(DMC_CUDA_ERR_UNSUPPORTED, "gemv: batched NK layout is not offered");
+        // several activation rows: a real contraction, which goes to the tensor cores.  Measured
+        // crossover on B200 at 4096x4096: with f32 activations (split in two bf16 terms) the tcgen05
+        // GEMM overtakes one GEMV per row from 3 rows up.
+        const int min_m = tuning().tc_min_m > 0 ? tuning().tc_min_m : 3;
+        if (m >= min_m && wdtype == DMC_W_BF16 && variant < 0 && !ctx().peer && gemm_tc_eligible(m, k, n, dW, dx))
+            return launch_gemm_tc_f32x(dW, dx, dy, m, k, n, stream);
         return launch_nk(dW, dx, dy, m, k, n, wdtype, variant, stream);
     }
     return fail(DMC_CUDA_ERR_BAD_ARG, "gemv: unknown layout %d", layout);

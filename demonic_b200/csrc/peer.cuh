@@ -1,12 +1,12 @@
 // peer.cuh -- output exchange fused into the GEMV kernel for the row-sharded path.
 //
-// Instead of a separate all-gather after the kernel, the GEMV's last CTA (the one that
-// sees every other CTA finished) pushes this rank's y slice into all `world` replicas
-// with plain st.global to peer-mapped memory over NVLink (loads never cross the link,
-// no multicast is involved), publishes this rank's epoch number in each peer's flag
-// word (release, system scope) and then waits -- with a bound -- until all peers have
-// published theirs, so completion of the kernel on a GPU means the whole replicated y
-// has landed there.
+// Instead of a separate all-gather after the kernel, every CTA of the GEMV pushes the
+// contiguous run of rows it computed into all `world` replicas of y with plain st.global
+// to peer-mapped memory over NVLink (loads never cross the link, no multicast is
+// involved).  The CTA that sees every other CTA finished then publishes this rank's epoch
+// number in each peer's flag word (release, system scope) and waits -- with a bound --
+// until all peers have published theirs, so completion of the kernel on a GPU means the
+// whole replicated y has landed there.
 //
 // y is double-buffered by epoch parity: a rank can be at most one exchange ahead of
 // a peer (it cannot finish epoch e+1 before the peer has signalled e+1), so writes of
@@ -49,13 +49,30 @@ __device__ __forceinline__ void peer_store(const PeerOut *p, unsigned e, long lo
     p->y[p->rank][(long long)(e & 1u) * p->stride + idx] = v;
 }
 
-// Called by every thread of every CTA after its last peer_store.  The CTA that arrives last
-// pushes this rank's finished slice y[yoff, yoff+count) to every peer with coalesced stores
-// (remote traffic as full 128-byte lines instead of one 4-byte packet per row), publishes the
+// Called by every thread of a CTA once all its warps have stored their rows (after a
+// __syncthreads): the CTA copies its own contiguous run y[first, first+count) of this rank's
+// replica into every peer's replica.  Every CTA pushes its own rows as soon as it has them, so
+// the NVLink traffic overlaps the CTAs that are still streaming weights.
+template <int THREADS>
+__device__ __forceinline__ void peer_push(const PeerOut *p, unsigned e, long long first, long long count) {
+    if (p->world <= 1 || (p->debug & 1)) return;
+    const long long base = (long long)(e & 1u) * p->stride + first;
+    const float *src = p->y[p->rank] + base;
+    bool wrote = false;
+    for (long long i = threadIdx.x; i < count; i += THREADS) {
+        const float v = __ldcg(src + i);
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r)
+            if (r < p->world && r != p->rank) p->y[r][base + i] = v;
+        wrote = true;
+    }
+    if (wrote) __threadfence_system();  // the remote stores are performed before this CTA reports in
+}
+
+// Called by every thread of every CTA after peer_push.  The CTA that arrives last publishes the
 // epoch in the peers' flag words and waits, bounded, for theirs.
 template <int THREADS>
-__device__ __forceinline__ void peer_finish(const PeerOut *p, unsigned e, long long yoff, long long count,
-                                            int *s_last) {
+__device__ __forceinline__ void peer_finish(const PeerOut *p, unsigned e, int *s_last) {
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -64,25 +81,8 @@ __device__ __forceinline__ void peer_finish(const PeerOut *p, unsigned e, long l
     }
     __syncthreads();
     if (!*s_last) return;
-    __threadfence();
+    __threadfence_system();
     const int t = threadIdx.x;
-    const long long base = (long long)(e & 1u) * p->stride + yoff;
-    const float *src = p->y[p->rank] + base;
-    if (p->world > 1 && !(p->debug & 1)) {
-        const bool vec = ((base | count) & 3) == 0;  // every replica has the same offset, so one test serves all
-        for (int r = 0; r < p->world; ++r) {
-            if (r == p->rank) continue;
-            float *dst = p->y[r] + base;
-            if (vec) {
-                const float4 *s4 = reinterpret_cast<const float4 *>(src);
-                float4 *d4 = reinterpret_cast<float4 *>(dst);
-                for (long long i = t; i < count / 4; i += THREADS) d4[i] = __ldcg(s4 + i);
-            } else {
-                for (long long i = t; i < count; i += THREADS) dst[i] = __ldcg(src + i);
-            }
-        }
-        __threadfence_system();  // each writer: its remote stores are visible before the flag below
-    }
     __syncthreads();
     if (t < p->world) st_release_sys(p->flags[t] + p->rank, e);  // tell rank t that our slice has landed
     if (t < p->world && !(p->debug & 2)) {

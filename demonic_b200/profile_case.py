@@ -22,6 +22,8 @@ def main() -> None:
     ap.add_argument("--launches", type=int, default=8)
     ap.add_argument("--variant", type=int, default=-1)
     ap.add_argument("--mib", type=int, default=256, help="distinct weight bytes to rotate over")
+    ap.add_argument("--m", type=int, default=1, help="activation rows")
+    ap.add_argument("--op", type=int, default=0, help="0 GEMV kernels, 1 tcgen05 GEMM (bf16 x), 2 tcgen05 GEMM (f32 x)")
     ap.add_argument("--param", action="append", default=[], help="tuning knob name=value")
     args = ap.parse_args()
     rows, cols = (int(t) for t in args.shape.split("x"))
@@ -31,16 +33,16 @@ def main() -> None:
         assert lib.dmc_cuda_set_param(name.encode(), int(val)) == 0, name
     rng = np.random.default_rng(synth.DEFAULT_SEED)
     w = synth.bf16_weights(rng, (rows, cols))
-    x = synth.activations(rng, (cols,))
+    x = synth.bf16_weights(rng, (args.m, cols)) if args.op == 1 else synth.activations(rng, (args.m, cols))
     copies = max(2, -(-(args.mib << 20) // w.nbytes))
     layout = backend.LAYOUT_NK if args.layout == "nk" else backend.LAYOUT_KN
     bufs = [backend.DeviceBuffer.from_host(w) for _ in range(copies)]
-    dx, dy = backend.DeviceBuffer.from_host(x), backend.DeviceBuffer(rows * 4)
-    items = [(bufs[i % copies], dx, dy, 1, cols, rows, layout, backend.W_BF16, args.variant)
+    dx, dy = backend.DeviceBuffer.from_host(x), backend.DeviceBuffer(args.m * rows * 4)
+    items = [(bufs[i % copies], dx, dy, args.m, cols, rows, layout, backend.W_BF16, args.variant, args.op)
              for i in range(args.launches)]
     us = backend.bench_items(items, steps=1, warmup=1, use_graph=False) / len(items)
-    b = synth.gemv_bytes(rows, cols)
-    print(f"{args.shape} {args.layout} variant={args.variant}: {us:.2f} us/launch, {b / us / 1e3:.0f} GB/s "
+    b = synth.gemv_bytes(rows, cols, m=args.m)
+    print(f"{args.shape} {args.layout} m={args.m} op={args.op} variant={args.variant}: {us:.2f} us/launch, {b / us / 1e3:.0f} GB/s "
           f"(algorithmic bytes {b})")
 
 

@@ -187,6 +187,7 @@ typedef struct dmc_gemv_item {
     float *y;
     int64_t m, k, n;
     int layout, wdtype, variant;
+    int op; /* 0: dmc_cuda_gemv_dev; 1: dmc_cuda_gemm_dev with bf16 x; 2: dmc_cuda_gemm_dev with f32 x */
 } dmc_gemv_item;
 
 /* Device-timed benchmark: a step is the `count` GEMVs of `items` launched back
