@@ -294,13 +294,9 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
     const int nvec = K / EPV;
     const uint4 *W4 = reinterpret_cast<const uint4 *>(a.W);
 
-    // Row groups of R rows.  Normally the groups are dealt round-robin over all warps of the grid
-    // (best balance); for the fused exchange a CTA takes one contiguous block of rows instead, so
-    // that it can push its finished rows to the peers as one run.
-    const bool block_rows = a.peer != nullptr;
-    const int rbeg = block_rows ? (int)(((long long)N * blockIdx.x) / gridDim.x) : 0;
-    const int rend = block_rows ? (int)(((long long)N * (blockIdx.x + 1)) / gridDim.x) : N;
-    const int rstride = block_rows ? WARPS * R : (int)gridDim.x * WARPS * R;
+    // groups of R rows are dealt round-robin over all warps of the grid
+    const int rend = N;
+    const int rstride = (int)gridDim.x * WARPS * R;
 
     uint4 w[R][U];
     auto load_w = [&](int row0, int c) {
@@ -337,7 +333,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
     };
 
     __shared__ int s_last;
-    int row0 = block_rows ? rbeg + warp * R : ((int)blockIdx.x * WARPS + warp) * R;
+    int row0 = ((int)blockIdx.x * WARPS + warp) * R;
     if (row0 < rend) load_w(row0, lane);
     griddep_launch_dependents();
     griddep_wait();
@@ -380,10 +376,6 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
                 else a.y[row] = s;
             }
         }
-    }
-    if (a.peer) {
-        __syncthreads();
-        peer_push<THREADS>(a.peer, epoch, a.yoff + rbeg, rend - rbeg);
     }
     if (a.peer) peer_finish<THREADS>(a.peer, epoch, &s_last);
 }

@@ -326,7 +326,7 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
     int cps = std::min(by_threads, by_smem);
     if (tuning().nk_ctas_per_sm > 0) cps = std::min(cps, tuning().nk_ctas_per_sm);
     const int64_t groups = (n + (int64_t)v.WARPS * v.R - 1) / ((int64_t)v.WARPS * v.R);
-    const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(groups, (int64_t)c.sm_count * cps));
+    int64_t grid = std::max<int64_t>(1, std::min<int64_t>(groups, (int64_t)c.sm_count * cps));
     a.peer = static_cast<const PeerOut *>(c.peer);
     a.yoff = c.peer_yoff;
     for (int64_t mi = 0; mi < m; ++mi) {

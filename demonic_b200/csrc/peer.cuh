@@ -1,9 +1,8 @@
 // peer.cuh -- output exchange fused into the GEMV kernel for the row-sharded path.
 //
-// Instead of a separate all-gather after the kernel, every CTA of the GEMV pushes the
-// contiguous run of rows it computed into all `world` replicas of y with plain st.global
-// to peer-mapped memory over NVLink (loads never cross the link, no multicast is
-// involved).  The CTA that sees every other CTA finished then publishes this rank's epoch
+// Instead of a separate all-gather after the kernel, the GEMV stores every output element
+// into all `world` replicas of y as soon as it is computed, with plain st.global to
+// peer-mapped memory over NVLink (loads never cross the link, no multicast is involved).  The CTA that sees every other CTA finished then publishes this rank's epoch
 // number in each peer's flag word (release, system scope) and waits -- with a bound --
 // until all peers have published theirs, so completion of the kernel on a GPU means the
 // whole replicated y has landed there.
@@ -43,37 +42,26 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
 // peer_finish of the last CTA, after every CTA has passed its arrival).
 __device__ __forceinline__ unsigned peer_epoch(const PeerOut *p) { return __ldcg(p->epoch) + 1u; }
 
-// During the kernel every CTA stores its outputs into this rank's own replica (ordinary
-// local stores); the exchange happens once, in peer_finish.
+// Each finished output element goes straight into every rank's replica: one local store and
+// world-1 remote stores, issued by the lane that holds the row's sum while the rest of the grid
+// is still streaming weights.  No fence here: the writers release at GPU scope (fence + arrival
+// counter in peer_finish) and the last CTA's system-scope fence and release are cumulative over
+// everything ordered before them.  (A system-scope fence per writer thread was measured at
+// ~15 us per kernel on B200.)
 __device__ __forceinline__ void peer_store(const PeerOut *p, unsigned e, long long idx, float v) {
-    p->y[p->rank][(long long)(e & 1u) * p->stride + idx] = v;
-}
-
-// Called by every thread of a CTA once all its warps have stored their rows (after a
-// __syncthreads): the CTA copies its own contiguous run y[first, first+count) of this rank's
-// replica into every peer's replica.  Every CTA pushes its own rows as soon as it has them, so
-// the NVLink traffic overlaps the CTAs that are still streaming weights.
-template <int THREADS>
-__device__ __forceinline__ void peer_push(const PeerOut *p, unsigned e, long long first, long long count) {
-    if (p->world <= 1 || (p->debug & 1)) return;
-    const long long base = (long long)(e & 1u) * p->stride + first;
-    const float *src = p->y[p->rank] + base;
-    bool wrote = false;
-    for (long long i = threadIdx.x; i < count; i += THREADS) {
-        const float v = __ldcg(src + i);
+    const long long off = (long long)(e & 1u) * p->stride + idx;
 #pragma unroll
-        for (int r = 0; r < kMaxPeers; ++r)
-            if (r < p->world && r != p->rank) p->y[r][base + i] = v;
-        wrote = true;
-    }
-    if (wrote) __threadfence_system();  // the remote stores are performed before this CTA reports in
+    for (int r = 0; r < kMaxPeers; ++r)
+        if (r < p->world && !((p->debug & 1) && r != p->rank)) p->y[r][off] = v;
 }
 
-// Called by every thread of every CTA after peer_push.  The CTA that arrives last publishes the
+// Called by every thread of every CTA after its last peer_store.  The CTA that arrives last publishes the
 // epoch in the peers' flag words and waits, bounded, for theirs.
 template <int THREADS>
 __device__ __forceinline__ void peer_finish(const PeerOut *p, unsigned e, int *s_last) {
-    __threadfence();
+    if (p->debug & 16) return;
+    // only the lanes that stored outputs (lane 0 of each warp) have anything to order
+    if ((threadIdx.x & 31) == 0) __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
         const unsigned total = gridDim.x * gridDim.y * gridDim.z;
@@ -81,10 +69,10 @@ __device__ __forceinline__ void peer_finish(const PeerOut *p, unsigned e, int *s
     }
     __syncthreads();
     if (!*s_last) return;
-    __threadfence_system();
+    __threadfence();  // acquire side of the arrival counter; the release below is at system scope
     const int t = threadIdx.x;
     __syncthreads();
-    if (t < p->world) st_release_sys(p->flags[t] + p->rank, e);  // tell rank t that our slice has landed
+    if (t < p->world && !(p->debug & 32)) st_release_sys(p->flags[t] + p->rank, e);  // tell rank t that our slice has landed
     if (t < p->world && !(p->debug & 2)) {
         const unsigned *mine = p->flags[p->rank] + t;
         const long long t0 = clock64();

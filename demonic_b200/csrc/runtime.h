@@ -94,7 +94,7 @@ struct Tuning {
     int tc_smem_kb = 0;     // tcgen05 GEMM: shared-memory ring budget per CTA
     int tc_min_m = 0;       // activation rows from which `@` goes to the tensor cores (0 = library default)
     int shard_debug = 0;
-    int shard_fused = 1;    // sharded GEMV: 1 = peer stores fused into the kernel, 0 = NCCL all-gather
+    int shard_fused = -1;   // sharded GEMV: 1 = peer stores fused into the kernel, 0 = NCCL all-gather, -1 = by world size
 };
 
 Context &ctx();

@@ -83,15 +83,17 @@ def run(args, rank: int, world: int) -> None:
     allt = [None] * world
     dist.all_gather_object(allt, t)
     us_max = max(v[0] for v in allt)
-    # the same step with the exchange done by ncclAllGather after the kernel, for comparison
-    lib.dmc_cuda_set_param(b"shard_fused", 0)
-    dist.barrier()
-    us_nccl = sharded.bench(bufs, dx, COLS, ROWS, args.steps, args.warmup, use_graph=True)
-    backend.sync()
-    lib.dmc_cuda_set_param(b"shard_fused", 1)
-    alln = [None] * world
-    dist.all_gather_object(alln, [us_nccl])
-    us_nccl_max = max(v[0] for v in alln)
+    # the same step with each exchange forced: fused into the kernel (peer stores + flags) and ncclAllGather
+    forced = {}
+    for name, mode in (("fused_peer_stores", 1), ("nccl_allgather", 0)):
+        lib.dmc_cuda_set_param(b"shard_fused", mode)
+        dist.barrier()
+        u = sharded.bench(bufs, dx, COLS, ROWS, args.steps, args.warmup, use_graph=True)
+        backend.sync()
+        allu = [None] * world
+        dist.all_gather_object(allu, [u])
+        forced[name] = max(v[0] for v in allu) / copies
+    lib.dmc_cuda_set_param(b"shard_fused", -1)
     alg = synth.gemv_bytes(ROWS, COLS)            # whole job: every weight byte once + x + y
     value = alg * copies / us_max / 1e3
 
@@ -118,16 +120,17 @@ def run(args, rank: int, world: int) -> None:
             "warmup": args.warmup, "ms_per_step": us_max / 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32 accumulate over bf16 weights", "data": "synthetic",
             "config": {"workload": f"row-sharded bf16 GEMV {ROWS}x{COLS} (BASELINE config 5), rows split evenly over "
-                                   f"{world} GPUs, output slices stored into every rank's replica of y by the GEMV kernel itself "
-                                   f"(peer stores over NVLink + flag exchange)",
+                                   f"{world} GPUs, output slices exchanged into a replicated y: "
+                                   + ("by the GEMV kernel itself (peer stores over NVLink + flag exchange)" if world >= 4
+                                      else "ncclAllGather after the kernel"),
                        "gemvs_per_step": copies, "rows_per_rank": r1 - r0,
                        "l2": f"inputs larger than L2: each rank rotates over {copies} distinct copies of its "
                              f"{w.nbytes >> 20} MiB shard",
-                       "launch": "one CUDA graph replay per step (one fused GEMV+exchange kernel per copy)",
+                       "launch": "one CUDA graph replay per step",
                        "timing": "CUDA events per rank on the launching stream, max over ranks"},
             "tflops": synth.gemv_flops(ROWS, COLS) * copies / us_max / 1e6,
             "us_per_sharded_gemv": us_max / copies,
-            "us_per_sharded_gemv_with_nccl_allgather": us_nccl_max / copies,
+            "us_per_sharded_gemv_by_exchange": forced,
             "frac_of_nominal_8tbs": value / (bench_mod.NOMINAL_HBM_GBS * world),
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": bench_mod.UNIT,
                          "frac": value / world / peak, "peak_kind": f"of {peak_kind}", "traffic": None,

@@ -31,10 +31,12 @@ def test_world_of_one_is_the_plain_gemv():
             lib.dmc_cuda_set_param(b"shard_fused", fused)
             sharded.gemv(dW, dx, k, n)
             assert_parity(sharded.output(n), ref, TOL_BF16, f"fused={fused}")
+        lib.dmc_cuda_set_param(b"shard_fused", 1)
         us = sharded.bench([dW], dx, k, n, steps=3, warmup=1)      # graph replays advance the epoch on the device
         assert us > 0
         sharded.gemv(dW, dx, k, n)
         assert_parity(sharded.output(n), ref, TOL_BF16, "after graph replays")
+        lib.dmc_cuda_set_param(b"shard_fused", -1)
     finally:
         sharded.shutdown()
     assert lib.dmc_cuda_status() == 0
@@ -67,6 +69,7 @@ for n in (8192, 1001):                      # even split (all-gather) and ragged
         y = sharded.output(n)
         err = float(np.max(np.abs(y - ref)) / np.max(np.abs(ref)))
         assert err < 1e-5, (rank, n, fused, err)
+    lib.dmc_cuda_set_param(b"shard_fused", 1)
     us = sharded.bench([dW], dx, k, n, steps=5, warmup=2)
     sharded.gemv(dW, dx, k, n)
     y = sharded.output(n)
