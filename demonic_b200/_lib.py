@@ -50,6 +50,12 @@ SIGNATURES = {
     "dmc_cuda_shard_output": (VP, []),
     "dmc_cuda_bench_shard": (C.c_double, [VP, C.c_int, VP, I64, I64, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_gemm_dev": (C.c_int, [VP, VP, VP, I64, I64, I64, C.c_int]),
+    "dmc_decoder_create": (C.c_int, [VP, C.POINTER(VP)]),
+    "dmc_decoder_load": (C.c_int, [VP, C.c_int, C.c_int, VP, I64]),
+    "dmc_decoder_step": (C.c_int, [VP, C.c_int, C.c_int, C.POINTER(C.c_int), VP]),
+    "dmc_decoder_bench": (C.c_double, [VP, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "dmc_decoder_launches_per_step": (I64, [VP]),
+    "dmc_decoder_destroy": (None, [VP]),
     "dmc_cuda_bench_items": (C.c_double, [VP, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_variant_count": (C.c_int, [C.c_int, C.c_int]),
     "dmc_cuda_variant_name": (C.c_char_p, [C.c_int, C.c_int, C.c_int]),
@@ -63,6 +69,14 @@ class GemvItem(C.Structure):
     """``dmc_gemv_item`` of include/dmc_cuda.h."""
     _fields_ = [("W", VP), ("x", VP), ("y", VP), ("m", I64), ("k", I64), ("n", I64),
                 ("layout", C.c_int), ("wdtype", C.c_int), ("variant", C.c_int), ("op", C.c_int)]
+
+
+
+
+class DecoderConfig(C.Structure):
+    """``dmc_decoder_config`` of include/dmc_cuda.h."""
+    _fields_ = [("layers", C.c_int), ("d_model", C.c_int), ("heads", C.c_int), ("head_dim", C.c_int),
+                ("ffn", C.c_int), ("vocab", C.c_int), ("max_len", C.c_int), ("eps", C.c_float)]
 
 
 _lib = None

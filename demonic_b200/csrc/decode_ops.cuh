@@ -1,0 +1,222 @@
+// decode_ops.cuh -- the small kernels around the GEMVs of one decode step of a decoder-only
+// transformer built from the reference's own ops.  Each restates the f32 form the JIT emits:
+//   rms_norm   compiler/src/jit.rs:23776-23847 (x * g / sqrt(mean(x^2) + eps))
+//   rope       docs/STDLIB.md:185-202, compiler/src/interp.rs:13636-13678 (pairs (2i, 2i+1))
+//   attention  compiler/src/jit.rs:20303-20506 (q.K^T, scale 1/sqrt(d), softmax, p.V) over a KV cache
+//   silu       compiler/src/interp.rs:13418 (x / (1 + e^-x)); SwiGLU = silu(gate) * up
+//   embed      compiler/src/interp.rs:13494-13516 (ids clamp to [0, V-1])
+//   argmax     compiler/src/interp.rs:13529-13538 (first strict maximum)
+// They are tolerance-matched companions (sums run in parallel, not sequentially), not
+// roofline-graded; all activations stay on the device between them.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gemv.cuh"
+
+namespace dmc {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Sum over a CTA of up to 1024 threads; every thread gets the total.
+__device__ __forceinline__ float block_sum(float v, float *red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int i = 0; i < nw; ++i) t += red[i];
+    return t;
+}
+
+// h[d] = widen(vocab[clamp(id)][d])
+__global__ void embed_kernel(const uint16_t *__restrict__ vocab, int V, int D, const int *__restrict__ id_ptr,
+                             float *__restrict__ h) {
+    griddep_wait();
+    int id = *id_ptr;
+    id = id < 0 ? 0 : (id > V - 1 ? V - 1 : id);
+    for (int d = blockIdx.x * blockDim.x + threadIdx.x; d < D; d += gridDim.x * blockDim.x)
+        h[d] = __uint_as_float((uint32_t)vocab[(size_t)id * D + d] << 16);
+}
+
+// y = x * g * rsqrt-free form of the JIT: inv = 1 / sqrt(sum(x^2)/d + eps).  One CTA.
+// If `add` is non-null the input is first updated in place: x += add (the residual connection).
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ add,
+                                                        const float *__restrict__ g, float *__restrict__ y, int D,
+                                                        float eps) {
+    __shared__ float red[32];
+    griddep_launch_dependents();
+    griddep_wait();
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = x[i];
+        if (add) {
+            v += add[i];
+            x[i] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    const float tot = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(tot / (float)D + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) y[i] = x[i] * g[i] * inv;
+}
+
+// RoPE on q and k (pairs (2i, 2i+1) of each head, angle row `pos` of the cos/sin tables) and the
+// KV-cache append: K[h][pos] = rope(k_h), V[h][pos] = v_h.  qkv = [q | k | v], each H*hd floats.
+// Cache layout [H][cap][hd] f32 (the reference's KV[B,H,~,D] with B = 1).
+__global__ void rope_append_kernel(float *__restrict__ qkv, const float *__restrict__ cs, const float *__restrict__ sn,
+                                   float *__restrict__ kc, float *__restrict__ vc, int H, int hd, int cap,
+                                   const int *__restrict__ pos_ptr) {
+    griddep_launch_dependents();
+    griddep_wait();
+    const int pos = *pos_ptr;
+    const int half = hd / 2, total = H * half;
+    float *q = qkv, *k = qkv + H * hd, *v = qkv + 2 * H * hd;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int h = i / half, p = i % half;
+        const float c = cs[(size_t)pos * half + p], s = sn[(size_t)pos * half + p];
+        const int e = h * hd + 2 * p;
+        const float qa = q[e], qb = q[e + 1];
+        q[e] = qa * c - qb * s;
+        q[e + 1] = qa * s + qb * c;
+        const float ka = k[e], kb = k[e + 1];
+        const size_t ce = ((size_t)h * cap + pos) * hd + 2 * p;
+        kc[ce] = ka * c - kb * s;
+        kc[ce + 1] = ka * s + kb * c;
+        vc[ce] = v[e];
+        vc[ce + 1] = v[e + 1];
+    }
+}
+
+// Decode attention, split over the keys: CTA (h, z) handles keys [z*chunk, (z+1)*chunk) of head h with an
+// online softmax, and leaves (max, sum, unnormalised output[hd]) for the combine kernel.  hd == 128:
+// a lane owns 4 dims, a warp one key at a time.  part layout [H][splits][hd + 2].
+__global__ void __launch_bounds__(128) attn_partial_kernel(const float *__restrict__ qkv, const float *__restrict__ kc,
+                                                            const float *__restrict__ vc, float *__restrict__ part,
+                                                            int H, int cap, const int *__restrict__ pos_ptr, int chunk) {
+    constexpr int HD = 128;
+    __shared__ float sm_m[4], sm_l[4], sm_o[4][HD];
+    griddep_launch_dependents();
+    griddep_wait();
+    const int len = *pos_ptr + 1;  // keys 0..pos (the new token was just appended)
+    const int h = blockIdx.x, z = blockIdx.y, splits = gridDim.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t0 = z * chunk, t1 = min(len, t0 + chunk);
+    const float scale = 1.0f / sqrtf((float)HD);
+    const float4 q4 = reinterpret_cast<const float4 *>(qkv + (size_t)h * HD)[lane];
+    float m = -INFINITY, l = 0.0f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int t = t0 + warp; t < t1; t += 4) {
+        const float4 k4 = __ldcs(reinterpret_cast<const float4 *>(kc + ((size_t)h * cap + t) * HD) + lane);
+        const float4 v4 = __ldcs(reinterpret_cast<const float4 *>(vc + ((size_t)h * cap + t) * HD) + lane);
+        float s = q4.x * k4.x + q4.y * k4.y + q4.z * k4.z + q4.w * k4.w;
+        s = warp_sum(s) * scale;
+        const float mn = fmaxf(m, s);
+        const float corr = __expf(m - mn), p = __expf(s - mn);
+        l = l * corr + p;
+        o.x = o.x * corr + p * v4.x;
+        o.y = o.y * corr + p * v4.y;
+        o.z = o.z * corr + p * v4.z;
+        o.w = o.w * corr + p * v4.w;
+        m = mn;
+    }
+    if (lane == 0) {
+        sm_m[warp] = m;
+        sm_l[warp] = l;
+    }
+    reinterpret_cast<float4 *>(sm_o[warp])[lane] = o;
+    __syncthreads();
+    // merge the four warps
+    float M = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+    const int d = threadIdx.x;  // 128 threads, one dim each
+    float L = 0.0f, O = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const float c = (sm_m[w] == -INFINITY) ? 0.0f : __expf(sm_m[w] - M);
+        L += sm_l[w] * c;
+        O += sm_o[w][d] * c;
+    }
+    float *dst = part + ((size_t)h * splits + z) * (HD + 2);
+    dst[d] = O;
+    if (d == 0) {
+        dst[HD] = M;
+        dst[HD + 1] = L;
+    }
+}
+
+// out[h][d] = sum_z O_z e^(m_z - M) / sum_z l_z e^(m_z - M)
+__global__ void __launch_bounds__(128) attn_combine_kernel(const float *__restrict__ part, float *__restrict__ out,
+                                                            int splits) {
+    constexpr int HD = 128;
+    griddep_launch_dependents();
+    griddep_wait();
+    const int h = blockIdx.x, d = threadIdx.x;
+    const float *p = part + (size_t)h * splits * (HD + 2);
+    float M = -INFINITY;
+    for (int z = 0; z < splits; ++z) M = fmaxf(M, p[(size_t)z * (HD + 2) + HD]);
+    float L = 0.0f, O = 0.0f;
+    for (int z = 0; z < splits; ++z) {
+        const float mz = p[(size_t)z * (HD + 2) + HD];
+        const float c = (mz == -INFINITY) ? 0.0f : __expf(mz - M);
+        L += p[(size_t)z * (HD + 2) + HD + 1] * c;
+        O += p[(size_t)z * (HD + 2) + d] * c;
+    }
+    out[(size_t)h * HD + d] = L > 0.0f ? O / L : 0.0f;
+}
+
+// act[i] = silu(gate[i]) * up[i], gu = [gate | up]
+__global__ void swiglu_kernel(const float *__restrict__ gu, float *__restrict__ act, int F) {
+    griddep_launch_dependents();
+    griddep_wait();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < F; i += gridDim.x * blockDim.x) {
+        const float g = gu[i];
+        act[i] = (g / (1.0f + __expf(-g))) * gu[F + i];
+    }
+}
+
+// First strict maximum of x[0..n); one CTA.
+__global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ x, int n, int *__restrict__ out) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    griddep_wait();
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = x[i];
+        if (v > best) {
+            best = v;
+            idx = i;
+        }
+    }
+    auto better = [](float v, int i, float bv_, int bi_) { return v > bv_ || (v == bv_ && i < bi_); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v2 = __shfl_xor_sync(0xffffffffu, best, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (better(v2, i2, best, idx)) {
+            best = v2;
+            idx = i2;
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) {
+        bv[warp] = best;
+        bi[warp] = idx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (better(bv[w], bi[w], bv[0], bi[0])) {
+                bv[0] = bv[w];
+                bi[0] = bi[w];
+            }
+        *out = bi[0] == 0x7fffffff ? 0 : bi[0];
+    }
+}
+
+}  // namespace dmc

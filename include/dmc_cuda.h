@@ -226,6 +226,37 @@ float *dmc_cuda_shard_output(void);
 double dmc_cuda_bench_shard(const void *const *dW_shards, int copies, const float *dx, int64_t k, int64_t n,
                             int wdtype, int steps, int warmup, int use_graph);
 
+/* ---- device-resident decode step ----------------------------------------------------------------
+ * One decode step (batch 1) of a decoder-only transformer made of the reference's own ops -- RMSNorm,
+ * RoPE, softmax attention over a KV cache, SwiGLU MLP (compiler/src/jit.rs:23776-23847, 24411-24530,
+ * 20303-20506; docs/STDLIB.md:185-202) -- with every projection on the GEMV path and all
+ * activations on the device, replayed from one CUDA graph.  The callers of the matmul path, kept
+ * off the host: no counterpart in the reference, whose decode loop crosses the host per matmul. */
+typedef struct dmc_decoder_config {
+    int layers, d_model, heads, head_dim, ffn, vocab, max_len; /* head_dim must be 128 */
+    float eps;                                                  /* RMSNorm epsilon */
+} dmc_decoder_config;
+
+/* Tensors of dmc_decoder_load.  Matrices are bf16 bits, [out][in] row-major (k contiguous): WQKV is
+ * [3*d_model][d_model] (q rows, then k, then v), WGU is [2*ffn][d_model] (gate rows, then up), WD is
+ * [d_model][ffn]; gains are f32 [d_model]; ROPE_COS / ROPE_SIN are f32 [max_len][head_dim/2]; KCACHE /
+ * VCACHE are f32 [heads][max_len][head_dim]. */
+enum {
+    DMC_DEC_EMBED = 0, DMC_DEC_WQKV = 1, DMC_DEC_WO = 2, DMC_DEC_WGU = 3, DMC_DEC_WD = 4, DMC_DEC_GAIN1 = 5,
+    DMC_DEC_GAIN2 = 6, DMC_DEC_GAIN_FINAL = 7, DMC_DEC_LM_HEAD = 8, DMC_DEC_ROPE_COS = 9, DMC_DEC_ROPE_SIN = 10,
+    DMC_DEC_KCACHE = 11, DMC_DEC_VCACHE = 12
+};
+
+int dmc_decoder_create(const dmc_decoder_config *cfg, void **out);
+int dmc_decoder_load(void *dec, int which, int layer, const void *host, int64_t bytes);
+/* Run one step: embed `token`, append its k/v at cache position `pos`, attend over keys 0..pos, return
+ * the arg-max token (and the f32 logits if `logits_out` is non-null).  Synchronous. */
+int dmc_decoder_step(void *dec, int token, int pos, int *next_token, float *logits_out);
+/* Device-timed microseconds per step over `steps` graph replays after `warmup` (token and pos fixed). */
+double dmc_decoder_bench(void *dec, int token, int pos, int steps, int warmup);
+int64_t dmc_decoder_launches_per_step(void *dec);
+void dmc_decoder_destroy(void *dec);
+
 /* Number of kernel configurations a layout/type offers, and a printable name. */
 int dmc_cuda_variant_count(int layout, int wdtype);
 const char *dmc_cuda_variant_name(int layout, int wdtype, int variant);

@@ -133,6 +133,19 @@ def gemm_bf16_fma(a, w_bits) -> np.ndarray:
     return c
 
 
+def gemm_bf16_nt(a, w_nk_bits) -> np.ndarray:
+    """`x @ w'` for w stored [n, k]: transpose (compiler/src/jit.rs:29801-29834) then the interpreter's
+    `@` (compiler/src/interp.rs:9270-9287), computed without materialising the transpose."""
+    a = _f32(a)
+    w = _u16(w_nk_bits)
+    m, k = a.shape
+    n, k2 = w.shape
+    assert k == k2
+    c = np.empty((m, n), np.float32)
+    lib().orc_gemm_bf16_nt(_p(a), _p(w), _p(c), _i64(m), _i64(k), _i64(n))
+    return c
+
+
 def dot_two_rounding(a, b_col) -> float:
     """compiler/src/jit.rs:37403-37412 — the non-contracted hand loop."""
     a = _f32(a)

@@ -119,6 +119,19 @@ ORC_API void orc_gemm_bf16_fma(const float *a, const uint16_t *b, float *c,
         }
 }
 
+/* `x @ w'` with w stored [n, k] (k contiguous): the same ascending-k fmaf chain per output element as
+ * orc_gemm_bf16_fma on the transposed weight -- what compiler/src/jit.rs:29801-29834 (transpose) followed
+ * by compiler/src/interp.rs:9270-9287 computes -- without materialising the transpose. */
+ORC_API void orc_gemm_bf16_nt(const float *a, const uint16_t *w, float *c, int64_t m, int64_t k, int64_t n) {
+    for (int64_t i = 0; i < m; i++)
+        for (int64_t j = 0; j < n; j++) {
+            float acc = 0.0f;
+            const uint16_t *wr = w + j * k;
+            for (int64_t kk = 0; kk < k; kk++) acc = fmaf(a[i * k + kk], bf16_widen(wr[kk]), acc);
+            c[i * n + j] = acc;
+        }
+}
+
 /* The "two-rounding" hand loop of compiler/src/jit.rs:37403-37412
  * (s = s + a*b, product rounded before the add); used only to pin that the
  * oracle contracts where the reference says it must. */
