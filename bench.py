@@ -257,6 +257,8 @@ def run_single(args) -> None:
            "host_cores": os.cpu_count(),
            "sample": f"{passes} passes over the five sweep shapes (~10 s), dmc_matmul_bf16 order and thread policy"}
 
+    extras = run_extras(args, lib, backend, synth, dev[0][2], peak)
+
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": us_step / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -278,7 +280,65 @@ def run_single(args) -> None:
         "gpu_launches": gpu_launches,
         "gpu_launches_including_warmup": launches_total,
     }
+    line.update(extras)
     print(json.dumps(line), flush=True)
+
+
+def run_extras(args, lib, backend, synth, w4096_bufs, hbm_peak) -> dict:
+    """The other single-GPU configurations, reported beside the headline (not part of `value`):
+    small-batch X @ W' with the GEMV -> tcgen05 crossover (config 3), the tcgen05 GEMM on a dense
+    contraction against the measured bf16 tensor peak, and one decode step (config 4)."""
+    out = {}
+    k = n = 4096
+    rng = np.random.default_rng(synth.DEFAULT_SEED + 77)
+    rows = []
+    for m in (1, 2, 4, 8, 16):
+        xb = synth.bf16_weights(rng, (m, k))                      # bf16 activations N(0, 0.02)
+        dXb = backend.DeviceBuffer.from_host(xb)
+        dXf = backend.DeviceBuffer.from_host(synth.bf16_to_f32(xb))
+        dY = backend.DeviceBuffer(m * n * 4)
+        alg = n * k * 2 + m * k * 2 + m * n * 4
+        us_gemv = backend.bench_items([(b, dXf, dY, m, k, n, backend.LAYOUT_NK, backend.W_BF16, 3) for b in w4096_bufs],
+                                      max(args.steps, 5), args.warmup) / len(w4096_bufs)
+        us_tc = backend.bench_items([(b, dXb, dY, m, k, n, backend.LAYOUT_NK, backend.W_BF16, -1, 1) for b in w4096_bufs],
+                                    max(args.steps, 5), args.warmup) / len(w4096_bufs)
+        best = min(us_gemv, us_tc)
+        rows.append({"n": m, "us_gemv_kernel_per_row": round(us_gemv, 2), "us_tcgen05_gemm": round(us_tc, 2),
+                     "winner": "gemv" if us_gemv <= us_tc else "tcgen05", "gbs": round(alg / best / 1e3, 1),
+                     "frac_of_measured_peak": round(alg / best / 1e3 / hbm_peak, 4)})
+    cross = next((r["n"] for r in rows if r["winner"] == "tcgen05"), None)
+    out["small_batch"] = {"workload": "X bf16 [N,4096] @ W' with W bf16 [4096,4096] (BASELINE config 3), f32 out",
+                          "rows": rows, "crossover_to_tcgen05_at_n": cross}
+    # dense contraction on the tensor cores
+    try:
+        tpeak = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        t_burst, t_kind = float(tpeak["bf16_tflops"]), "measured"
+    except Exception:
+        t_burst, t_kind = 1590.0, "fallback"
+    M = 8192
+    dW = backend.DeviceBuffer.from_host(synth.bf16_weights(rng, (M, M)))
+    dX = backend.DeviceBuffer.from_host(synth.bf16_weights(rng, (M, M)))
+    dY = backend.DeviceBuffer(M * M * 4)
+    us = backend.bench_items([(dW, dX, dY, M, M, M, backend.LAYOUT_NK, backend.W_BF16, -1, 1)], 5, 2)
+    tf = 2.0 * M * M * M / us / 1e6
+    out["dense_gemm"] = {"workload": "bf16 8192^3 X @ W' on tcgen05/TMEM, f32 out", "us": round(us, 1),
+                         "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": t_burst, "unit": "TFLOP/s",
+                                      "frac": round(tf / t_burst, 4), "peak_kind": f"of {t_kind} (cuBLAS burst)"}}
+    for b in (dW, dX, dY):
+        b.free()
+    # one decode step (config 4)
+    from demonic_b200 import decoder
+    cfg = decoder.Config()
+    dec = decoder.Decoder(cfg, decoder.random_model(cfg, cache_len=512))
+    us = dec.bench(1234, 512, max(args.steps, 20), args.warmup)
+    byt = cfg.weight_bytes() + cfg.kv_bytes(513)
+    out["decode"] = {"workload": "one decode step, 8 layers, d_model 2048, 16x128 heads, FFN 5632, vocab 32000, bf16 weights, "
+                                 "KV length 512 (+ the new token), batch 1 (BASELINE config 4), device resident, one CUDA graph",
+                     "us_per_step": round(us, 1), "tokens_per_s": round(1e6 / us, 1), "launches_per_step": dec.launches_per_step,
+                     "bytes_per_step": byt, "gbs": round(byt / us / 1e3, 1), "frac_of_measured_peak": round(byt / us / 1e3 / hbm_peak, 4),
+                     "tokens_per_s_bound_at_measured_peak": round(hbm_peak * 1e9 / byt, 1)}
+    dec.close()
+    return out
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture of the 4096x4096 case
