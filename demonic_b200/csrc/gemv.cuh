@@ -282,7 +282,12 @@ __global__ void __launch_bounds__(TK * 32) gemv_kn_generic_kernel(const GemvArgs
 // step), then reduces across lanes with shuffles.  CTAs stride over row groups.
 // Needs K % EPV == 0 and a 16-byte aligned W.  Dynamic shared memory: K floats
 // rounded up to a multiple of 256.
-template <int WARPS, int R, int U, typename WT>
+// XG = true reads x straight from global memory (L1-cached, after the dependency wait) instead of
+// staging it in shared memory: no prologue copy, no barrier, no shared memory.
+// PF > 0 additionally requests the next PF chunks of a warp's first row group with cp.async into
+// shared memory before the dependency wait (the first chunk is already in registers), so that for
+// short rows the whole matrix is in flight while the previous kernel is still running.
+template <int WARPS, int R, int U, typename WT, bool XG = false, int PF = 0>
 __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
     constexpr int EPV = VecOf<WT>::EPV;
     constexpr int THREADS = WARPS * 32;
@@ -318,7 +323,11 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
             const int cc = c + 32 * u;
             float4 xa = make_float4(0, 0, 0, 0), xb = xa;
             if (cc < nvec) {
-                if constexpr (EPV == 8) {
+                if constexpr (XG) {
+                    const float4 *xg = reinterpret_cast<const float4 *>(a.x) + (size_t)cc * (EPV / 4);
+                    xa = xg[0];
+                    if constexpr (EPV == 8) xb = xg[1];
+                } else if constexpr (EPV == 8) {
                     // block of 32 vectors = 64 float4: low halves first, then high halves
                     const int blk = cc >> 5, l = cc & 31;
                     xa = xs4[blk * 64 + l];
@@ -335,13 +344,35 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
     __shared__ int s_last;
     int row0 = ((int)blockIdx.x * WARPS + warp) * R;
     if (row0 < rend) load_w(row0, lane);
+    // prefetch area: [warp][chunk 1..PF][R][U][lane] 16-byte slots after the x staging area
+    uint4 *pf = nullptr;
+    if constexpr (PF > 0) {
+        const size_t xs_bytes = XG ? 0 : (size_t)((K + 255) / 256 * 256) * sizeof(float);
+        pf = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(xs) + xs_bytes) + (size_t)warp * (PF * R * U * 32);
+        if (row0 < rend) {
+#pragma unroll
+            for (int p = 0; p < PF; ++p)
+#pragma unroll
+                for (int j = 0; j < R; ++j)
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int cc = lane + (p + 1) * 32 * U + 32 * u, row = row0 + j;
+                        if (row < rend && cc < nvec)
+                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(
+                                             &pf[((p * R + j) * U + u) * 32 + lane])),
+                                         "l"(W4 + (size_t)row * nvec + cc)
+                                         : "memory");
+                    }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     griddep_launch_dependents();
     griddep_wait();
     // after the wait: the previous exchange (an earlier kernel) is what advances the epoch word
     const unsigned epoch = a.peer ? peer_epoch(a.peer) : 0u;
 
     // stage x (after the dependency wait: an earlier kernel may produce it)
-    {
+    if constexpr (!XG) {
         const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
         const int n4 = K / 4;
         for (int i = threadIdx.x; i < n4; i += THREADS) {
@@ -353,18 +384,33 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
                 xs4[i] = v;
             }
         }
+        __syncthreads();
     }
-    __syncthreads();
 
-    bool first = true;
+    bool first = true;  // the warp's first row group: chunk 0 is in registers, chunks 1..PF in shared memory
     for (; row0 < rend; row0 += rstride) {
 #pragma unroll
         for (int j = 0; j < R; ++j) acc[j] = 0.0f;
-        for (int c = lane; c < nvec; c += 32 * U) {
-            if (!first) load_w(row0, c);
-            first = false;
+        int it = 0;
+        for (int c = lane; c < nvec; c += 32 * U, ++it) {
+            if (first && it == 0) {
+                // already loaded before the dependency wait
+            } else if (PF > 0 && first && it <= PF) {
+                if (it == 1) asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < R; ++j)
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int cc = c + 32 * u;
+                        w[j][u] = (row0 + j < rend && cc < nvec) ? pf[(((it - 1) * R + j) * U + u) * 32 + lane]
+                                                                 : make_uint4(0, 0, 0, 0);
+                    }
+            } else {
+                load_w(row0, c);
+            }
             consume(c);
         }
+        first = false;
 #pragma unroll
         for (int j = 0; j < R; ++j) {
             float s = acc[j];

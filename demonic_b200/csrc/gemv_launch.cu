@@ -52,16 +52,31 @@ struct NkVariant {
     const char *name;
     int WARPS, R, U;
     KernelFn bf16, f32;
+    bool xg;  // x read from global memory (no shared-memory staging)
+    int pf;   // chunks of the first row group prefetched through shared memory before the dependency wait
 };
 #define NK_ROW(WARPS, R, U)                                                       \
     {                                                                             \
         "nk_w" #WARPS "_r" #R "_u" #U, WARPS, R, U,                               \
-            gemv_nk_kernel<WARPS, R, U, uint16_t>, gemv_nk_kernel<WARPS, R, U, float> \
+            gemv_nk_kernel<WARPS, R, U, uint16_t>, gemv_nk_kernel<WARPS, R, U, float>, false, 0 \
+    }
+#define NK_ROWG(WARPS, R, U)                                                                  \
+    {                                                                                         \
+        "nk_w" #WARPS "_r" #R "_u" #U "_xg", WARPS, R, U,                                     \
+            gemv_nk_kernel<WARPS, R, U, uint16_t, true>, gemv_nk_kernel<WARPS, R, U, float, true>, true, 0 \
+    }
+#define NK_ROWPF(WARPS, R, U, PF)                                                             \
+    {                                                                                         \
+        "nk_w" #WARPS "_r" #R "_u" #U "_pf" #PF, WARPS, R, U,                                 \
+            gemv_nk_kernel<WARPS, R, U, uint16_t, false, PF>, gemv_nk_kernel<WARPS, R, U, float, false, PF>, false, PF \
     }
 static const NkVariant kNk[] = {
     NK_ROW(8, 2, 4),  NK_ROW(8, 1, 4),  NK_ROW(8, 1, 8),  NK_ROW(8, 2, 8),
     NK_ROW(8, 4, 4),  NK_ROW(16, 1, 4), NK_ROW(16, 2, 4), NK_ROW(16, 1, 8),
     NK_ROW(4, 2, 8),  NK_ROW(4, 4, 4),  NK_ROW(8, 4, 2),  NK_ROW(16, 2, 2),
+    NK_ROWG(8, 2, 8), NK_ROWG(8, 1, 16), NK_ROWG(16, 1, 8), NK_ROWG(8, 2, 4), NK_ROWG(4, 2, 8), NK_ROWG(8, 4, 4),
+    NK_ROWG(4, 1, 16), NK_ROWG(16, 2, 4),
+    NK_ROWPF(8, 2, 8, 1), NK_ROWPF(8, 2, 4, 3), NK_ROWPF(8, 1, 8, 1), NK_ROWPF(16, 1, 8, 1),
 };
 constexpr int kNkCount = sizeof(kNk) / sizeof(kNk[0]);
 
@@ -121,9 +136,10 @@ int default_kn_variant(int64_t k, int64_t n) {
     return 3;
 }
 int default_nk_variant(int64_t k, int64_t n) {
-    (void)k;
-    (void)n;
-    return 3;
+    // B200 sweeps: 8 warps x 2 rows x 8 loads in flight is within ~2 % of the best configuration on
+    // every decode shape; long rows of a big matrix do a little better with 4 rows x 4 loads.
+    if (k >= 8192 && n >= 8192) return 4;  // nk_w8_r4_u4
+    return 3;                              // nk_w8_r2_u8
 }
 
 int launch_kn(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
@@ -274,7 +290,7 @@ int launch_nk_tma(const TmaPlan &p, const void *dW, const float *dx, float *dy, 
         a.x = dx + mi * k;
         a.y = dy + mi * n;
         void *params[] = {&a};
-        int rc = launch_ex((const void *)fn, dim3((unsigned)grid), dim3((p.cw + 1) * 32), p.smem, stream, params);
+        int rc = launch_ex((const void *)fn, dim3((unsigned)grid), dim3((p.cw + 2) * 32), p.smem, stream, params);
         if (rc) return rc;
     }
     return DMC_CUDA_OK;
@@ -321,8 +337,10 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
                                           200 * 1024));
         attr_set[wdtype][variant] = true;
     }
+    const size_t smem_used = (v.xg ? 0 : smem) + (size_t)v.pf * v.WARPS * v.R * v.U * 512;
+    if (smem_used > 200 * 1024) return fail(DMC_CUDA_ERR_UNSUPPORTED, "gemv: variant %s needs too much shared memory for k=%lld", v.name, (long long)k);
     int by_threads = 2048 / (v.WARPS * 32);
-    int by_smem = (int)std::max<size_t>(1, (220 * 1024) / (smem + 1024));
+    int by_smem = (int)std::max<size_t>(1, (220 * 1024) / (smem_used + 1024));
     int cps = std::min(by_threads, by_smem);
     if (tuning().nk_ctas_per_sm > 0) cps = std::min(cps, tuning().nk_ctas_per_sm);
     const int64_t groups = (n + (int64_t)v.WARPS * v.R - 1) / ((int64_t)v.WARPS * v.R);
@@ -333,7 +351,7 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
         a.x = dx + mi * k;
         a.y = dy + mi * n;
         void *params[] = {&a};
-        int rc = launch_ex((const void *)fn, dim3((unsigned)grid), dim3(v.WARPS * 32), smem, stream, params);
+        int rc = launch_ex((const void *)fn, dim3((unsigned)grid), dim3(v.WARPS * 32), smem_used, stream, params);
         if (rc) return rc;
     }
     return DMC_CUDA_OK;

@@ -16,9 +16,11 @@
 // kernel (x is read once per CTA: lane l of warp w owns the 16-byte vectors
 // v = i*CW*32 + w*32 + l of every row), reads W from shared memory with
 // conflict-free 128-bit loads, and reduces four rows at a time with a shared
-// butterfly.  Per stage the CW warp partials meet in shared memory; the warp
-// that arrives last adds them in a fixed order (results do not vary run to
-// run), stores y and hands the stage back to the producer.
+// butterfly.  Per stage the CW warp partials meet in shared memory; a reducer warp
+// adds them in a fixed order (results do not vary run to run), stores y and hands
+// the stage back to the producer, so the consumers never wait on one another.
+// (Measured on B200 it reaches 4.5-6.0 TB/s, behind the LDG kernel of gemv.cuh on the
+// decode shapes, which therefore stays the default; this one is selectable as a variant.)
 //
 // Every wait is bounded: a wait that runs out records a code in *err and the
 // CTA leaves; nothing spins forever.
@@ -63,13 +65,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *b, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait; false when the limit ran out.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(b)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; false when the limit ran out.  Polls with the non-blocking test_wait: the
+// potentially-blocking try_wait parks the thread for a scheduler-defined interval, which a
+// pipeline whose stages last well under a microsecond cannot afford.
 __device__ __forceinline__ bool mbar_wait(uint64_t *b, uint32_t parity) {
-    if (mbar_try_wait(b, parity)) return true;
+    if (mbar_test_wait(b, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(b, parity))
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_test_wait(b, parity)) return true;
         if (clock64() - t0 > kSpinCycles) return false;
-    return true;
+    }
 }
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -79,13 +95,13 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
 }
 
 // Dynamic shared memory: S*stage_bytes (ring) + S*SR*CW floats (warp partials).
+// Warps: CW consumers, one reducer (warp CW), one producer (warp CW+1).
 template <int VPL, int CW, typename WT>
-__global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_nk_tma_kernel(const GemvTmaArgs a) {
+__global__ void __launch_bounds__((CW + 2) * 32, 1) gemv_nk_tma_kernel(const GemvTmaArgs a) {
     constexpr int EPV = VecOf<WT>::EPV;
     constexpr int RU = 4;  // rows reduced together
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ uint64_t full[kTmaMaxStages], empty[kTmaMaxStages];
-    __shared__ int cnt[kTmaMaxStages];
+    __shared__ uint64_t full[kTmaMaxStages], empty[kTmaMaxStages], done[kTmaMaxStages];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int N = a.N, K = a.K, S = a.S, SR = a.SR;
@@ -97,7 +113,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_nk_tma_kernel(const Gem
         for (int s = 0; s < S; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
-            cnt[s] = 0;
+            mbar_init(&done[s], CW);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -108,7 +124,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_nk_tma_kernel(const Gem
     const int r1 = (int)(((long long)N * (blockIdx.x + 1)) / gridDim.x);
     const int nchunks = (r1 - r0 + SR - 1) / SR;
 
-    if (warp == CW) {  // ---- producer ----
+    griddep_launch_dependents();
+
+    if (warp == CW + 1) {  // ---- producer: never waits for the previous kernel, weights are constant ----
         if (lane == 0) {
             const unsigned char *Wb = reinterpret_cast<const unsigned char *>(a.W);
             for (int c = 0; c < nchunks; ++c) {
@@ -121,19 +139,39 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_nk_tma_kernel(const Gem
                 const int rows = min(SR, r1 - row0);
                 const uint32_t bytes = (uint32_t)(rows * rowbytes);
                 mbar_expect_tx(&full[s], bytes);
-                // copies of at most 32 KiB each
                 const unsigned char *src = Wb + (size_t)row0 * rowbytes;
                 unsigned char *dst = smem + (size_t)s * a.stage_bytes;
                 for (uint32_t off = 0; off < bytes; off += 32768u)
                     bulk_g2s(dst + off, src + off, min(32768u, bytes - off), &full[s]);
             }
         }
-        griddep_launch_dependents();
+        return;
+    }
+
+    if (warp == CW) {  // ---- reducer: adds the CW partials of each row in a fixed order, stores y ----
+        griddep_wait();  // y may still be read by the previous kernel
+        for (int c = 0; c < nchunks; ++c) {
+            const int s = c % S;
+            if (!mbar_wait(&done[s], (c / S) & 1)) {
+                *(volatile int *)a.err = 7;
+                return;
+            }
+            const int row0 = r0 + c * SR;
+            const int rows = min(SR, r1 - row0);
+            const float *spart = part + (size_t)s * SR * CW;
+            for (int r = lane; r < rows; r += 32) {
+                float sum = 0.0f;
+#pragma unroll
+                for (int w = 0; w < CW; ++w) sum += spart[r * CW + w];
+                a.y[row0 + r] = sum;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);  // ring slot and its partials are free again
+        }
         return;
     }
 
     // ---- consumers ----
-    griddep_launch_dependents();
     griddep_wait();  // x may be produced by the previous kernel in the stream
     float xr[VPL][8];
 #pragma unroll
@@ -146,6 +184,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_nk_tma_kernel(const Gem
             if constexpr (EPV == 8) {
                 float4 hi = __ldcg(xp + 1);
                 xr[i][4] = hi.x, xr[i][5] = hi.y, xr[i][6] = hi.z, xr[i][7] = hi.w;
+            } else {
+                xr[i][4] = xr[i][5] = xr[i][6] = xr[i][7] = 0.0f;
             }
         } else {
 #pragma unroll
@@ -159,8 +199,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_nk_tma_kernel(const Gem
             *(volatile int *)a.err = 2;
             return;
         }
-        const int row0 = r0 + c * SR;
-        const int rows = min(SR, r1 - row0);
+        const int rows = min(SR, r1 - (r0 + c * SR));
         const unsigned char *stage = smem + (size_t)s * a.stage_bytes;
         float *spart = part + (size_t)s * SR * CW;
 
@@ -171,17 +210,20 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_nk_tma_kernel(const Gem
 #pragma unroll
             for (int i = 0; i < VPL; ++i) {
                 const int v = i * (CW * 32) + warp * 32 + lane;
+                // all loads of the batch first (rows past the chunk / vectors past the row read a
+                // valid address and are discarded), then the arithmetic
+                const int vv = v < nvec ? v : 0;
+                uint4 wv[RU];
+#pragma unroll
+                for (int j = 0; j < RU; ++j) {
+                    const int rj = rb + j < rows ? rb + j : rb;
+                    wv[j] = *reinterpret_cast<const uint4 *>(stage + (size_t)rj * rowbytes + (size_t)vv * 16);
+                }
+                const float4 xa = make_float4(xr[i][0], xr[i][1], xr[i][2], xr[i][3]);
+                const float4 xb = make_float4(xr[i][4], xr[i][5], xr[i][6], xr[i][7]);
                 if (v < nvec) {
 #pragma unroll
-                    for (int j = 0; j < RU; ++j) {
-                        if (rb + j < rows) {
-                            const uint4 wv =
-                                *reinterpret_cast<const uint4 *>(stage + (size_t)(rb + j) * rowbytes + (size_t)v * 16);
-                            const float4 xa = make_float4(xr[i][0], xr[i][1], xr[i][2], xr[i][3]);
-                            const float4 xb = make_float4(xr[i][4], xr[i][5], xr[i][6], xr[i][7]);
-                            acc[j] = dot_vec<WT>(acc[j], wv, xa, xb);
-                        }
-                    }
+                    for (int j = 0; j < RU; ++j) acc[j] = dot_vec<WT>(acc[j], wv[j], xa, xb);
                 }
             }
             // butterfly over 4 rows: 6 shuffles instead of 20
@@ -199,30 +241,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_nk_tma_kernel(const Gem
             const int rr = rb + ((lane >> 4) << 1) + ((lane >> 3) & 1);
             if ((lane & 7) == 0 && rr < rows) spart[rr * CW + warp] = kk;
         }
-
-        // last warp to finish the stage combines the CW partials per row in a fixed order
         __syncwarp();
-        int last = 0;
-        if (lane == 0) {
-            __threadfence_block();
-            last = (atomicAdd(&cnt[s], 1) == CW - 1);
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-            __threadfence_block();
-            for (int r = lane; r < rows; r += 32) {
-                float sum = 0.0f;
-#pragma unroll
-                for (int w = 0; w < CW; ++w) sum += spart[r * CW + w];
-                a.y[row0 + r] = sum;
-            }
-            __syncwarp();
-            if (lane == 0) {
-                cnt[s] = 0;
-                __threadfence_block();
-                mbar_arrive(&empty[s]);
-            }
-        }
+        if (lane == 0) mbar_arrive(&done[s]);  // release: the reducer's wait sees this warp's partials
     }
 }
 
