@@ -4,6 +4,7 @@
 // per-call host<->device traffic the reference ABI forces (compiler/src/gpu.rs:528-531, 649-651)
 // disappears: a token id goes in, a token id comes out.
 #include <cstring>
+#include <utility>
 #include <vector>
 
 #include "decode_ops.cuh"
@@ -23,10 +24,16 @@ struct Decoder {
     std::vector<Layer> layers;
     uint16_t *embed = nullptr, *lm_head = nullptr;  // [V,D] bf16
     float *gf = nullptr, *rope_cos = nullptr, *rope_sin = nullptr;
+    float *h2 = nullptr;        // second residual-stream buffer (the fused RMSNorm ping-pongs between h and h2)
+    unsigned *attn_cnt = nullptr;
+    float *am_val = nullptr;    // argmax per-CTA candidates
+    int *am_idx = nullptr;
+    unsigned *am_cnt = nullptr;
+    int fused = 1;              // 1: RMSNorm / SwiGLU fused into the GEMVs' staging, RoPE + append + combine into attention
     float *h = nullptr, *xn = nullptr, *qkv = nullptr, *ao = nullptr, *d1 = nullptr, *gu = nullptr, *act = nullptr,
           *d2 = nullptr, *logits = nullptr, *part = nullptr;
     int *d_token = nullptr, *d_pos = nullptr, *d_next = nullptr;
-    int splits = 8;
+    int splits = 32;            // key ranges per head in the attention kernels
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     int64_t launches_per_step = 0;
@@ -45,8 +52,57 @@ int launch_small(void (*fn)(Args...), dim3 grid, dim3 block, cudaStream_t s, Arg
     return launch_ex((const void *)fn, grid, block, 0, s, params);
 }
 
-// All launches of one step, in order, on `s`.
-int enqueue_step(Decoder &d, cudaStream_t s) {
+// y = W . prologue(x) with the prologue fused into the GEMV's x staging (see GemvArgs::pro).
+int gemv_pro(const void *W, const float *x, float *y, int64_t k, int64_t n, int pro, const float *add, const float *g,
+             float *hout, float eps, cudaStream_t s) {
+    Context &c = ctx();
+    c.pro = pro;
+    c.pro_add = add;
+    c.pro_g = g;
+    c.pro_hout = hout;
+    c.pro_eps = eps;
+    int rc = launch_gemv(W, x, y, 1, k, n, 1, 0, 0, DMC_LAYOUT_NK, DMC_W_BF16, -1, s);
+    c.pro = 0;
+    c.pro_add = c.pro_g = nullptr;
+    c.pro_hout = nullptr;
+    return rc;
+}
+
+// All launches of one step, in order, on `s`: 5 per layer (43 in all for 8 layers).
+int enqueue_step_fused(Decoder &d, cudaStream_t s) {
+    const dmc_decoder_config &c = d.cfg;
+    const int D = c.d_model, H = c.heads, F = c.ffn, V = c.vocab, cap = c.max_len;
+    int rc;
+    float *hin = d.h, *hout = d.h2;
+    if ((rc = launch_small(embed_kernel, dim3(8), dim3(256), s, (const uint16_t *)d.embed, V, D, (const int *)d.d_token, hin)))
+        return rc;
+    const float *carry = nullptr;
+    const int chunk = (cap + d.splits - 1) / d.splits;
+    for (int l = 0; l < c.layers; ++l) {
+        Layer &L = d.layers[l];
+        // qkv = Wqkv . rms_norm(h + carry);  h' = h + carry
+        if ((rc = gemv_pro(L.wqkv, hin, d.qkv, D, 3 * D, (tuning().decode_debug & 4) ? 0 : 1, carry, L.g1, hout, c.eps, s))) return rc;
+        std::swap(hin, hout);
+        if (!(tuning().decode_debug & 1))
+        if ((rc = launch_small(attn_fused_kernel, dim3(H, d.splits), dim3(128), s, (const float *)d.qkv,
+                               (const float *)d.rope_cos, (const float *)d.rope_sin, L.kc, L.vc, d.part, d.ao, d.attn_cnt, H,
+                               cap, (const int *)d.d_pos, chunk)))
+            return rc;
+        if ((rc = launch_gemv(L.wo, d.ao, d.d1, 1, D, D, 1, 0, 0, DMC_LAYOUT_NK, DMC_W_BF16, -1, s))) return rc;
+        // gu = Wgu . rms_norm(h + d1);  h' = h + d1
+        if ((rc = gemv_pro(L.wgu, hin, d.gu, D, 2 * F, 1, d.d1, L.g2, hout, c.eps, s))) return rc;
+        std::swap(hin, hout);
+        // d2 = Wd . (silu(gate) * up)
+        if ((rc = gemv_pro(L.wd, d.gu, d.d2, F, D, 2, nullptr, nullptr, nullptr, 0.0f, s))) return rc;
+        carry = d.d2;
+    }
+    if ((rc = gemv_pro(d.lm_head, hin, d.logits, D, V, 1, carry, d.gf, nullptr, c.eps, s))) return rc;
+    if (tuning().decode_debug & 2) return DMC_CUDA_OK;
+    return launch_small(argmax_kernel, dim3(64), dim3(256), s, (const float *)d.logits, V, d.d_next, d.am_val, d.am_idx, d.am_cnt);
+}
+
+// The unfused sequence (9 launches per layer), kept as the reference arrangement of the same math.
+int enqueue_step_plain(Decoder &d, cudaStream_t s) {
     const dmc_decoder_config &c = d.cfg;
     const int D = c.d_model, H = c.heads, hd = c.head_dim, F = c.ffn, V = c.vocab, cap = c.max_len;
     int rc;
@@ -75,8 +131,10 @@ int enqueue_step(Decoder &d, cudaStream_t s) {
     }
     if ((rc = launch_small(rmsnorm_kernel, dim3(1), dim3(1024), s, d.h, carry, (const float *)d.gf, d.xn, D, c.eps))) return rc;
     if ((rc = launch_gemv(d.lm_head, d.xn, d.logits, 1, D, V, 1, 0, 0, DMC_LAYOUT_NK, DMC_W_BF16, -1, s))) return rc;
-    return launch_small(argmax_kernel, dim3(1), dim3(1024), s, (const float *)d.logits, V, d.d_next);
+    return launch_small(argmax_kernel, dim3(64), dim3(256), s, (const float *)d.logits, V, d.d_next, d.am_val, d.am_idx, d.am_cnt);
 }
+
+int enqueue_step(Decoder &d, cudaStream_t s) { return d.fused ? enqueue_step_fused(d, s) : enqueue_step_plain(d, s); }
 
 int ensure_graph(Decoder &d) {
     if (d.exec) return DMC_CUDA_OK;
@@ -137,7 +195,9 @@ extern "C" int dmc_decoder_create(const dmc_decoder_config *cfg, void **out) {
          dalloc(&d->rope_sin, cap * hd / 2) || dalloc(&d->h, D) || dalloc(&d->xn, D) || dalloc(&d->qkv, 3 * D) ||
          dalloc(&d->ao, D) || dalloc(&d->d1, D) || dalloc(&d->gu, 2 * F) || dalloc(&d->act, F) || dalloc(&d->d2, D) ||
          dalloc(&d->logits, V) || dalloc(&d->part, H * (size_t)d->splits * (hd + 2)) || dalloc(&d->d_token, 1) ||
-         dalloc(&d->d_pos, 1) || dalloc(&d->d_next, 1);
+         dalloc(&d->d_pos, 1) || dalloc(&d->d_next, 1) || dalloc(&d->h2, D) || dalloc(&d->attn_cnt, H) ||
+         dalloc(&d->am_val, 64) || dalloc(&d->am_idx, 64) || dalloc(&d->am_cnt, 1);
+    d->fused = tuning().decode_fused;
     for (Layer &L : d->layers)
         rc = rc || dalloc(&L.wqkv, 3 * D * D) || dalloc(&L.wo, D * D) || dalloc(&L.wgu, 2 * F * D) || dalloc(&L.wd, D * F) ||
              dalloc(&L.g1, D) || dalloc(&L.g2, D) || dalloc(&L.kc, H * cap * hd) || dalloc(&L.vc, H * cap * hd);
@@ -242,7 +302,7 @@ extern "C" void dmc_decoder_destroy(void *dec) {
     if (d->exec) cudaGraphExecDestroy(d->exec);
     if (d->graph) cudaGraphDestroy(d->graph);
     void *singles[] = {d->embed, d->lm_head, d->gf, d->rope_cos, d->rope_sin, d->h, d->xn, d->qkv, d->ao, d->d1, d->gu,
-                       d->act, d->d2, d->logits, d->part, d->d_token, d->d_pos, d->d_next};
+                       d->act, d->d2, d->logits, d->part, d->d_token, d->d_pos, d->d_next, d->h2, d->attn_cnt, d->am_val, d->am_idx, d->am_cnt};
     for (void *p : singles)
         if (p) cudaFree(p);
     for (Layer &L : d->layers) {

@@ -169,6 +169,134 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float *__restri
     out[(size_t)h * HD + d] = L > 0.0f ? O / L : 0.0f;
 }
 
+// The three kernels above in one launch: CTA (h, z) rotates q_h itself, the CTA whose key range
+// holds `pos` rotates and appends the new k/v (and uses them from shared memory), every CTA runs the
+// online softmax over its keys, and the CTA that arrives last at the head's counter merges the
+// splits into out[h].  cnt: one counter per head, zero between launches.
+__global__ void __launch_bounds__(128) attn_fused_kernel(const float *__restrict__ qkv, const float *__restrict__ cs,
+                                                          const float *__restrict__ sn, float *__restrict__ kc,
+                                                          float *__restrict__ vc, float *__restrict__ part,
+                                                          float *__restrict__ out, unsigned *__restrict__ cnt, int H, int cap,
+                                                          const int *__restrict__ pos_ptr, int chunk) {
+    constexpr int HD = 128;
+    __shared__ __align__(16) float qs[HD], ks[HD], vs[HD];
+    __shared__ float sm_m[4], sm_l[4];
+    __shared__ __align__(16) float sm_o[4][HD];
+    __shared__ int s_last;
+    griddep_launch_dependents();
+    const int h = blockIdx.x, z = blockIdx.y, splits = gridDim.y;
+    const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
+    const int t0 = z * chunk;
+    constexpr int KU = 4;
+    griddep_wait();
+    const int pos = *pos_ptr, len = pos + 1;
+    const int t1 = min(len, t0 + chunk);
+    const bool owns_new = pos >= t0 && pos < t0 + chunk;
+    {   // RoPE, pairs (2i, 2i+1): thread d holds element d and reads its partner
+        const float c = cs[(size_t)pos * (HD / 2) + (d >> 1)], s = sn[(size_t)pos * (HD / 2) + (d >> 1)];
+        const float *q = qkv + (size_t)h * HD, *k = qkv + (size_t)(H + h) * HD, *v = qkv + (size_t)(2 * H + h) * HD;
+        const float qa = q[d & ~1], qb = q[d | 1];
+        qs[d] = (d & 1) ? qa * s + qb * c : qa * c - qb * s;
+        if (owns_new) {
+            const float ka = k[d & ~1], kb = k[d | 1];
+            const float kr = (d & 1) ? ka * s + kb * c : ka * c - kb * s;
+            ks[d] = kr;
+            vs[d] = v[d];
+            kc[((size_t)h * cap + pos) * HD + d] = kr;
+            vc[((size_t)h * cap + pos) * HD + d] = v[d];
+        }
+    }
+    __syncthreads();
+    const float scale = 1.0f / sqrtf((float)HD);
+    const float4 q4 = reinterpret_cast<const float4 *>(qs)[lane];
+    float m = -INFINITY, l = 0.0f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    // KU keys in flight per warp: the loop is bound by memory latency, not by arithmetic
+    for (int tb = t0 + warp; tb < t1; tb += 4 * KU) {
+        float4 k4[KU], v4[KU];
+#pragma unroll
+        for (int u = 0; u < KU; ++u) {
+            const int t = tb + 4 * u;
+            if (t >= t1) {
+                k4[u] = v4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            } else if (t == pos) {
+                k4[u] = reinterpret_cast<const float4 *>(ks)[lane];
+                v4[u] = reinterpret_cast<const float4 *>(vs)[lane];
+            } else {
+                k4[u] = __ldcg(reinterpret_cast<const float4 *>(kc + ((size_t)h * cap + t) * HD) + lane);
+                v4[u] = __ldcg(reinterpret_cast<const float4 *>(vc + ((size_t)h * cap + t) * HD) + lane);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < KU; ++u) {
+            if (tb + 4 * u >= t1) break;
+            float s = q4.x * k4[u].x + q4.y * k4[u].y + q4.z * k4[u].z + q4.w * k4[u].w;
+            s = warp_sum(s) * scale;
+            const float mn = fmaxf(m, s);
+            const float corr = __expf(m - mn), p = __expf(s - mn);
+            l = l * corr + p;
+            o.x = o.x * corr + p * v4[u].x;
+            o.y = o.y * corr + p * v4[u].y;
+            o.z = o.z * corr + p * v4[u].z;
+            o.w = o.w * corr + p * v4[u].w;
+            m = mn;
+        }
+    }
+    if (lane == 0) {
+        sm_m[warp] = m;
+        sm_l[warp] = l;
+    }
+    reinterpret_cast<float4 *>(sm_o[warp])[lane] = o;
+    __syncthreads();
+    const float M = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+    float L = 0.0f, O = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const float c = (sm_m[w] == -INFINITY) ? 0.0f : __expf(sm_m[w] - M);
+        L += sm_l[w] * c;
+        O += sm_o[w][d] * c;
+    }
+    float *dst = part + ((size_t)h * splits + z) * (HD + 2);
+    dst[d] = O;
+    if (d == 0) {
+        dst[HD] = M;
+        dst[HD + 1] = L;
+    }
+    // last CTA of the head merges the splits (in split order: fixed)
+    __threadfence();
+    __syncthreads();
+    if (d == 0) s_last = (atomicAdd(&cnt[h], 1u) == (unsigned)splits - 1u);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // splits <= 32: one warp holds a (max, sum) pair per lane, the weights e^(m_z - M) go through
+    // shared memory, then every thread sums its dimension with the loads of all splits in flight
+    const float *p = part + (size_t)h * splits * (HD + 2);
+    __shared__ float cz[32], Lsum;
+    if (warp == 0) {
+        const float mz = lane < splits ? __ldcg(&p[(size_t)lane * (HD + 2) + HD]) : -INFINITY;
+        const float lz = lane < splits ? __ldcg(&p[(size_t)lane * (HD + 2) + HD + 1]) : 0.0f;
+        float Mx = mz;
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) Mx = fmaxf(Mx, __shfl_xor_sync(0xffffffffu, Mx, o2));
+        const float c = (mz == -INFINITY) ? 0.0f : __expf(mz - Mx);
+        cz[lane] = c;
+        const float Ls = warp_sum(lz * c);
+        if (lane == 0) Lsum = Ls;
+    }
+    __syncthreads();
+    float Os = 0.0f;
+    for (int z0 = 0; z0 < splits; z0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = (z0 + u < splits) ? __ldcg(&p[(size_t)(z0 + u) * (HD + 2) + d]) : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) Os += v[u] * cz[(z0 + u) & 31];
+    }
+    out[(size_t)h * HD + d] = Lsum > 0.0f ? Os / Lsum : 0.0f;
+    if (d == 0) cnt[h] = 0u;
+}
+
 // act[i] = silu(gate[i]) * up[i], gu = [gate | up]
 __global__ void swiglu_kernel(const float *__restrict__ gu, float *__restrict__ act, int F) {
     griddep_launch_dependents();
@@ -179,43 +307,74 @@ __global__ void swiglu_kernel(const float *__restrict__ gu, float *__restrict__ 
     }
 }
 
-// First strict maximum of x[0..n); one CTA.
-__global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ x, int n, int *__restrict__ out) {
-    __shared__ float bv[32];
-    __shared__ int bi[32];
+// First strict maximum of x[0..n) (ties: lowest index).  gridDim.x CTAs scan slices; the CTA that
+// arrives last at `cnt` merges the per-CTA candidates.  scratch: gridDim.x (value, index) pairs.
+__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ x, int n, int *__restrict__ out,
+                                                      float *__restrict__ sval, int *__restrict__ sidx,
+                                                      unsigned *__restrict__ cnt) {
+    __shared__ float bv[8];
+    __shared__ int bi[8];
+    __shared__ int s_last;
     griddep_wait();
+    auto better = [](float v, int i, float bv_, int bi_) { return v > bv_ || (v == bv_ && i < bi_); };
+    auto block_best = [&](float &best, int &idx) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float v2 = __shfl_xor_sync(0xffffffffu, best, o);
+            const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (better(v2, i2, best, idx)) {
+                best = v2;
+                idx = i2;
+            }
+        }
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        __syncthreads();
+        if (lane == 0) {
+            bv[warp] = best;
+            bi[warp] = idx;
+        }
+        __syncthreads();
+        best = bv[0];
+        idx = bi[0];
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (better(bv[w], bi[w], best, idx)) {
+                best = bv[w];
+                idx = bi[w];
+            }
+    };
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = x[i];
-        if (v > best) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float v = __ldcg(x + i);
+        if (better(v, i, best, idx)) {
             best = v;
             idx = i;
         }
     }
-    auto better = [](float v, int i, float bv_, int bi_) { return v > bv_ || (v == bv_ && i < bi_); };
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float v2 = __shfl_xor_sync(0xffffffffu, best, o);
-        const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (better(v2, i2, best, idx)) {
-            best = v2;
-            idx = i2;
-        }
-    }
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) {
-        bv[warp] = best;
-        bi[warp] = idx;
+    block_best(best, idx);
+    if (threadIdx.x == 0) {
+        sval[blockIdx.x] = best;
+        sidx[blockIdx.x] = idx;
+        __threadfence();
+        s_last = (atomicAdd(cnt, 1u) == gridDim.x - 1u);
     }
     __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    best = -INFINITY;
+    idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) {
+        const float v = __ldcg(sval + i);
+        const int j = __ldcg(sidx + i);
+        if (better(v, j, best, idx)) {
+            best = v;
+            idx = j;
+        }
+    }
+    block_best(best, idx);
     if (threadIdx.x == 0) {
-        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
-            if (better(bv[w], bi[w], bv[0], bi[0])) {
-                bv[0] = bv[w];
-                bi[0] = bi[w];
-            }
-        *out = bi[0] == 0x7fffffff ? 0 : bi[0];
+        *out = idx == 0x7fffffff ? 0 : idx;
+        *cnt = 0u;
     }
 }
 

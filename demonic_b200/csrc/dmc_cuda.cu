@@ -498,6 +498,8 @@ static int apply_param(const char *name, int64_t value) {
     else if (!strcmp(name, "nk_default")) t.nk_default = (int)value;
     else if (!strcmp(name, "shard_fused")) t.shard_fused = (int)value;
     else if (!strcmp(name, "shard_debug")) t.shard_debug = (int)value;
+    else if (!strcmp(name, "decode_fused")) t.decode_fused = (int)value;
+    else if (!strcmp(name, "decode_debug")) t.decode_debug = (int)value;
     else if (!strcmp(name, "tc_ksplit")) t.tc_ksplit = (int)value;
     else if (!strcmp(name, "tc_smem_kb")) t.tc_smem_kb = (int)value;
     else if (!strcmp(name, "tc_min_m")) t.tc_min_m = (int)value;

@@ -33,6 +33,13 @@ struct GemvArgs {
     long long ls, rs;    // batch strides in elements (x: f32, W: weight elements)
     const PeerOut *peer; // NK kernel, sharded path: store y into every rank's replica (else null)
     long long yoff;      // first row of this rank's slice within the replicated y
+    // NK kernel: an elementwise op applied to x while it is staged into shared memory (0 = none)
+    //   1  x = rms_norm(x + add) * g; CTA 0 also stores the sum x + add to hout (the residual stream)
+    //   2  x[i] = silu(x[i]) * x[K + i]  (SwiGLU over a [gate | up] vector of 2K floats)
+    int pro;
+    const float *pro_add, *pro_g;
+    float *pro_hout;
+    float pro_eps;
 };
 
 // ---- small device helpers ---------------------------------------------------
@@ -375,14 +382,59 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
     if constexpr (!XG) {
         const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
         const int n4 = K / 4;
-        for (int i = threadIdx.x; i < n4; i += THREADS) {
-            float4 v = __ldcg(x4 + i);
+        auto slot = [&](int i) -> float4 & {
             if constexpr (EPV == 8) {
                 const int blk = i >> 6, idx = i & 63;
-                xs4[blk * 64 + (idx & 1) * 32 + (idx >> 1)] = v;
+                return xs4[blk * 64 + (idx & 1) * 32 + (idx >> 1)];
             } else {
-                xs4[i] = v;
+                return xs4[i];
             }
+        };
+        if (a.pro == 1) {
+            // RMSNorm of the residual stream fused into the staging (f32 form of the JIT,
+            // compiler/src/jit.rs:23776-23847): every CTA normalises its own copy of x
+            __shared__ float red[WARPS];
+            const float4 *add4 = reinterpret_cast<const float4 *>(a.pro_add);
+            float4 *h4 = reinterpret_cast<float4 *>(a.pro_hout);
+            float ss = 0.0f;
+            for (int i = threadIdx.x; i < n4; i += THREADS) {
+                float4 v = __ldcg(x4 + i);
+                if (add4) {
+                    const float4 d = __ldcg(add4 + i);
+                    v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
+                }
+                if (h4 && blockIdx.x == 0) h4[i] = v;
+                ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+                slot(i) = v;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) red[warp] = ss;
+            __syncthreads();
+            float tot = 0.0f;
+#pragma unroll
+            for (int w2 = 0; w2 < WARPS; ++w2) tot += red[w2];
+            const float inv = 1.0f / sqrtf(tot / (float)K + a.pro_eps);
+            const float4 *g4 = reinterpret_cast<const float4 *>(a.pro_g);
+            for (int i = threadIdx.x; i < n4; i += THREADS) {  // each thread rescales what it stored itself
+                float4 v = slot(i);
+                const float4 g = __ldg(g4 + i);
+                v.x = v.x * g.x * inv, v.y = v.y * g.y * inv, v.z = v.z * g.z * inv, v.w = v.w * g.w * inv;
+                slot(i) = v;
+            }
+        } else if (a.pro == 2) {
+            // SwiGLU (silu = x / (1 + e^-x), compiler/src/interp.rs:13418) of a [gate | up] vector
+            for (int i = threadIdx.x; i < n4; i += THREADS) {
+                const float4 g = __ldcg(x4 + i), u = __ldcg(x4 + n4 + i);
+                float4 v;
+                v.x = g.x / (1.0f + __expf(-g.x)) * u.x;
+                v.y = g.y / (1.0f + __expf(-g.y)) * u.y;
+                v.z = g.z / (1.0f + __expf(-g.z)) * u.z;
+                v.w = g.w / (1.0f + __expf(-g.w)) * u.w;
+                slot(i) = v;
+            }
+        } else {
+            for (int i = threadIdx.x; i < n4; i += THREADS) slot(i) = __ldcg(x4 + i);
         }
         __syncthreads();
     }

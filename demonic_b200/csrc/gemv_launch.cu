@@ -303,6 +303,10 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
     const size_t smem = (size_t)((k + 255) / 256 * 256) * sizeof(float);
     const bool vec_ok = k % epv == 0 && ((uintptr_t)dW % 16) == 0 && ((uintptr_t)dx % 16) == 0 &&
                         smem <= 200 * 1024;
+    if (c.pro) {
+        if (!vec_ok) return fail(DMC_CUDA_ERR_UNSUPPORTED, "gemv: fused prologue needs k %% %d == 0 and aligned buffers", epv);
+        if (variant < 0 || variant >= kNkCount || kNk[variant].xg) variant = default_nk_variant(k, n);
+    }
     if (c.peer) {  // fused exchange lives in the vectorised LDG kernel only
         if (!vec_ok || m != 1)
             return fail(DMC_CUDA_ERR_UNSUPPORTED, "sharded gemv: needs m == 1, k %% %d == 0 and aligned buffers", epv);
@@ -347,6 +351,14 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
     int64_t grid = std::max<int64_t>(1, std::min<int64_t>(groups, (int64_t)c.sm_count * cps));
     a.peer = static_cast<const PeerOut *>(c.peer);
     a.yoff = c.peer_yoff;
+    if (c.pro) {
+        if (v.xg || m != 1) return fail(DMC_CUDA_ERR_UNSUPPORTED, "gemv: fused prologue needs the staged kernel and m == 1");
+        a.pro = c.pro;
+        a.pro_add = c.pro_add;
+        a.pro_g = c.pro_g;
+        a.pro_hout = c.pro_hout;
+        a.pro_eps = c.pro_eps;
+    }
     for (int64_t mi = 0; mi < m; ++mi) {
         a.x = dx + mi * k;
         a.y = dy + mi * n;
@@ -397,7 +409,7 @@ int launch_gemv(const void *dW, const float *dx, float *dy, int64_t m, int64_t k
         // crossover on B200 at 4096x4096: with f32 activations (split in two bf16 terms) the tcgen05
         // GEMM overtakes one GEMV per row from 3 rows up.
         const int min_m = tuning().tc_min_m > 0 ? tuning().tc_min_m : 3;
-        if (m >= min_m && wdtype == DMC_W_BF16 && variant < 0 && !ctx().peer && gemm_tc_eligible(m, k, n, dW, dx))
+        if (m >= min_m && wdtype == DMC_W_BF16 && variant < 0 && !ctx().peer && !ctx().pro && gemm_tc_eligible(m, k, n, dW, dx))
             return launch_gemm_tc_f32x(dW, dx, dy, m, k, n, stream);
         return launch_nk(dW, dx, dy, m, k, n, wdtype, variant, stream);
     }

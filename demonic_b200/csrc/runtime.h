@@ -76,6 +76,12 @@ struct Context {
     const void *peer = nullptr;  // device pointer to a PeerOut
     long long peer_yoff = 0;
 
+    // set by the decode step around a launch: elementwise prologue of the NK kernel's x staging
+    int pro = 0;
+    const float *pro_add = nullptr, *pro_g = nullptr;
+    float *pro_hout = nullptr;
+    float pro_eps = 0.0f;
+
     int64_t launches = 0;
 };
 
@@ -93,6 +99,8 @@ struct Tuning {
     int tc_ksplit = 0;      // tcgen05 GEMM: K splits (0 = derive from the tile count)
     int tc_smem_kb = 0;     // tcgen05 GEMM: shared-memory ring budget per CTA
     int tc_min_m = 0;       // activation rows from which `@` goes to the tensor cores (0 = library default)
+    int decode_fused = 1;   // decode step: fuse the companions into the GEMVs / attention (0 = one kernel per op)
+    int decode_debug = 0;   // measurement only: 1 = skip attention, 2 = skip argmax, 4 = no fused norm on the qkv GEMV
     int shard_debug = 0;
     int shard_fused = -1;   // sharded GEMV: 1 = peer stores fused into the kernel, 0 = NCCL all-gather, -1 = by world size
 };

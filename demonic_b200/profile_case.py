@@ -24,6 +24,7 @@ def main() -> None:
     ap.add_argument("--mib", type=int, default=256, help="distinct weight bytes to rotate over")
     ap.add_argument("--m", type=int, default=1, help="activation rows")
     ap.add_argument("--op", type=int, default=0, help="0 GEMV kernels, 1 tcgen05 GEMM (bf16 x), 2 tcgen05 GEMM (f32 x)")
+    ap.add_argument("--decode", type=int, default=0, help="run this many decode steps of the benchmark model instead")
     ap.add_argument("--param", action="append", default=[], help="tuning knob name=value")
     args = ap.parse_args()
     rows, cols = (int(t) for t in args.shape.split("x"))
@@ -31,6 +32,14 @@ def main() -> None:
     for kv in args.param:
         name, val = kv.split("=")
         assert lib.dmc_cuda_set_param(name.encode(), int(val)) == 0, name
+    if args.decode:
+        from . import decoder
+        cfg = decoder.Config()
+        dec = decoder.Decoder(cfg, decoder.random_model(cfg, cache_len=512))
+        for _ in range(args.decode):
+            tok = dec.step(1234, 512)
+        print(f"decode: {args.decode} steps, {dec.launches_per_step} launches per step, next token {tok}")
+        return
     rng = np.random.default_rng(synth.DEFAULT_SEED)
     w = synth.bf16_weights(rng, (rows, cols))
     x = synth.bf16_weights(rng, (args.m, cols)) if args.op == 1 else synth.activations(rng, (args.m, cols))

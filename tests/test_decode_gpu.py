@@ -11,6 +11,16 @@ from tests.parity import assert_parity
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[1, 0], ids=["fused", "one_kernel_per_op"], autouse=True)
+def arrangement(request):
+    """Both launch sequences of the same step: companions fused into the GEMVs / attention, or one kernel per op."""
+    lib = _lib.load()
+    lib.dmc_cuda_clear_error()
+    lib.dmc_cuda_set_param(b"decode_fused", request.param)
+    yield
+    lib.dmc_cuda_set_param(b"decode_fused", 1)
+
+
 def run_case(cfg, cache_len, tokens):
     model = decoder.random_model(cfg, seed=99, cache_len=cache_len)
     ref_model = copy.deepcopy(model)
