@@ -317,10 +317,15 @@ static int run_host_call(const HostCall &h) {
 
     memcpy(c.h_x + x_base, h.l, x_elems * 4);
     DMC_CUDA_TRY(cudaMemcpyAsync(c.d_x + x_base, c.h_x + x_base, x_elems * 4, cudaMemcpyHostToDevice, c.stream));
-    rc = launch_gemv(dW, (const float *)(c.d_x + x_base), (float *)(c.d_y + y_base), h.m, h.k, h.n, h.batch,
+    // Outputs are small (4n bytes): by default the kernel stores them straight into the pinned host
+    // mirror (device-visible through unified addressing), which saves the device->host copy and its
+    // launch latency on every call; "zero_copy_y" = 0 goes through the device buffer and a copy.
+    const bool zc = g_tuning.zero_copy_y != 0;
+    float *y_target = zc ? (float *)(c.h_y + y_base) : (float *)(c.d_y + y_base);
+    rc = launch_gemv(dW, (const float *)(c.d_x + x_base), y_target, h.m, h.k, h.n, h.batch,
                      h.ls, h.rs, layout, h.wdtype, -1, c.stream);
     if (rc) return rc;
-    DMC_CUDA_TRY(cudaMemcpyAsync(c.h_y + y_base, c.d_y + y_base, y_elems * 4, cudaMemcpyDeviceToHost, c.stream));
+    if (!zc) DMC_CUDA_TRY(cudaMemcpyAsync(c.h_y + y_base, c.d_y + y_base, y_elems * 4, cudaMemcpyDeviceToHost, c.stream));
 
     if (h.defer) {
         c.pending.push_back(PendingReadback{(const float *)(c.h_y + y_base), h.out, y_elems});
@@ -498,6 +503,7 @@ static int apply_param(const char *name, int64_t value) {
     else if (!strcmp(name, "nk_default")) t.nk_default = (int)value;
     else if (!strcmp(name, "shard_fused")) t.shard_fused = (int)value;
     else if (!strcmp(name, "shard_debug")) t.shard_debug = (int)value;
+    else if (!strcmp(name, "zero_copy_y")) t.zero_copy_y = (int)value;
     else if (!strcmp(name, "decode_fused")) t.decode_fused = (int)value;
     else if (!strcmp(name, "decode_debug")) t.decode_debug = (int)value;
     else if (!strcmp(name, "tc_ksplit")) t.tc_ksplit = (int)value;

@@ -99,6 +99,7 @@ struct Tuning {
     int tc_ksplit = 0;      // tcgen05 GEMM: K splits (0 = derive from the tile count)
     int tc_smem_kb = 0;     // tcgen05 GEMM: shared-memory ring budget per CTA
     int tc_min_m = 0;       // activation rows from which `@` goes to the tensor cores (0 = library default)
+    int zero_copy_y = 1;    // host-pointer entry points: kernels store y directly into pinned host memory
     int decode_fused = 1;   // decode step: fuse the companions into the GEMVs / attention (0 = one kernel per op)
     int decode_debug = 0;   // measurement only: 1 = skip attention, 2 = skip argmax, 4 = no fused norm on the qkv GEMV
     int shard_debug = 0;
