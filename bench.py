@@ -164,6 +164,35 @@ def run_reference(args, shapes, workload: str, rank: int, world: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def cpu_blas_baseline(host, alg_bytes: int) -> dict:
+    """cblas_sgemm(RowMajor, NoTrans, NoTrans, 1, n, k) on the widened [k, n] weights, ~5 s."""
+    from demonic_b200 import synth
+    cases = []
+    for w_nk, x in host:
+        w_kn = np.ascontiguousarray(synth.bf16_to_f32(w_nk).T)          # [k, n] f32, as `x @ w` sees it
+        cases.append((x.reshape(1, -1), w_kn, np.empty((1, w_kn.shape[1]), np.float32)))
+    threads, lib_name = None, "unknown"
+    try:
+        from threadpoolctl import threadpool_info
+        for info in threadpool_info():
+            if info.get("user_api") == "blas":
+                threads, lib_name = info.get("num_threads"), f"{info.get('internal_api')} {info.get('version')}"
+    except Exception:
+        pass
+    for x, w, out in cases:
+        np.matmul(x, w, out=out)
+    t0 = time.perf_counter()
+    passes = 0
+    while time.perf_counter() - t0 < 5.0:
+        for x, w, out in cases:
+            np.matmul(x, w, out=out)
+        passes += 1
+    dt = (time.perf_counter() - t0) / passes
+    return {"value": alg_bytes / dt / 1e9, "unit": UNIT, "cores": threads, "kind": "port", "blas": lib_name,
+            "note": "GB/s counted on the bf16 algorithmic bytes; the BLAS itself streams the 2x larger f32 copy",
+            "sample": f"{passes} passes over the five sweep shapes (~5 s), np.matmul -> sgemm on f32-widened [k, n] weights"}
+
+
 # --------------------------------------------------------------------------------------------
 # our arm, one GPU
 
@@ -257,6 +286,10 @@ def run_single(args) -> None:
            "host_cores": os.cpu_count(),
            "sample": f"{passes} passes over the five sweep shapes (~10 s), dmc_matmul_bf16 order and thread policy"}
 
+    # ---- the `--blas` form of the CPU path: sgemm on f32-widened weights (--blas applies to f32 x f32
+    # only, compiler/src/jit.rs:20811, 29375-29400), through the BLAS bundled with NumPy ----
+    cpu_blas = cpu_blas_baseline(host, e2e_bytes)
+
     extras = run_extras(args, lib, backend, synth, dev[0][2], peak)
 
     line = {
@@ -276,6 +309,7 @@ def run_single(args) -> None:
         "shapes": shapes_out,
         "e2e": e2e,
         "cpu_baseline": cpu,
+        "cpu_blas": cpu_blas,
         "clocks": clocks.summary(),
         "gpu_launches": gpu_launches,
         "gpu_launches_including_warmup": launches_total,
@@ -342,10 +376,10 @@ def run_extras(args, lib, backend, synth, w4096_bufs, hbm_peak) -> dict:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture of the 4096x4096 case
-# summarised in profiles/gemv_nk_ldg_4096x4096_full.md (33,587,712 B against 33,587,200 algorithmic:
-# ratio 1.00002), scaled to the sweep's mean launch by the algorithmic bytes (traffic is the weight
+# summarised in profiles/gemv_nk_ldg_4096x4096_full.md (33,614,592 B against 33,587,200 algorithmic:
+# ratio 1.0008), scaled to the sweep's mean launch by the algorithmic bytes (traffic is the weight
 # stream, which grows in proportion).
-TRAFFIC_RATIO = 33587712 / 33587200
+TRAFFIC_RATIO = 33614592 / 33587200
 
 
 def main() -> None:

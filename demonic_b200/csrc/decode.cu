@@ -1,6 +1,6 @@
 // decode.cu -- one decode step of a decoder-only transformer, fully on the device: every
 // projection goes through the GEMV path, the companions of decode_ops.cuh sit between them, and
-// the whole step (76 launches) is captured once into a CUDA graph and replayed per token, so the
+// the whole step (43 launches in the fused arrangement) is captured once into a CUDA graph and replayed per token, so the
 // per-call host<->device traffic the reference ABI forces (compiler/src/gpu.rs:528-531, 649-651)
 // disappears: a token id goes in, a token id comes out.
 #include <cstring>
