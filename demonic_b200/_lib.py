@@ -56,6 +56,9 @@ SIGNATURES = {
     "dmc_decoder_bench": (C.c_double, [VP, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dmc_decoder_launches_per_step": (I64, [VP]),
     "dmc_decoder_destroy": (None, [VP]),
+    "dmc_npz_locate": (C.c_int, [C.c_char_p, C.c_char_p, VP]),
+    "dmc_cuda_load_npz": (C.c_int, [C.c_char_p, C.c_char_p, I64, I64, C.c_int, C.c_int, C.c_int, I64, C.POINTER(VP),
+                                    C.POINTER(I64)]),
     "dmc_cuda_bench_items": (C.c_double, [VP, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_variant_count": (C.c_int, [C.c_int, C.c_int]),
     "dmc_cuda_variant_name": (C.c_char_p, [C.c_int, C.c_int, C.c_int]),
@@ -63,6 +66,12 @@ SIGNATURES = {
     "dmc_cuda_launch_count": (I64, []),
 }
 
+
+
+class NpzEntry(C.Structure):
+    """``dmc_npz_entry`` of include/dmc_cuda.h."""
+    _fields_ = [("data_offset", I64), ("data_bytes", I64), ("shape", I64 * 4), ("ndim", C.c_int),
+                ("itemsize", C.c_int), ("fortran_order", C.c_int), ("method", C.c_int), ("descr", C.c_char * 16)]
 
 
 class GemvItem(C.Structure):

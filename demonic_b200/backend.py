@@ -118,6 +118,36 @@ class DeviceBuffer:
             pass
 
 
+def npz_locate(path: str, key: str) -> dict:
+    """Describe entry ``key`` of a ``.npz`` archive (``dmc_npz_locate``; host only, no device)."""
+    e = _lib.NpzEntry()
+    rc = _lib.load().dmc_npz_locate(str(path).encode(), key.encode(), C.byref(e))
+    if rc != 0:
+        raise OSError(f"vault.load_npz: cannot locate `{key}` in `{path}` (status {rc})")
+    return {"data_offset": e.data_offset, "data_bytes": e.data_bytes, "shape": tuple(e.shape[:e.ndim]),
+            "itemsize": e.itemsize, "fortran_order": bool(e.fortran_order), "method": e.method,
+            "descr": e.descr.decode()}
+
+
+def load_npz(path: str, key: str, rows: int, cols: int, wdtype: int = W_BF16, rank: int = 0, world: int = 1,
+             host_dst: np.ndarray | None = None) -> tuple[DeviceBuffer, int]:
+    """``vault.load_npz`` straight into HBM (``dmc_cuda_load_npz``): returns the device buffer holding
+    this rank's rows of the ``[rows, cols]`` array and the number of rows loaded.  With ``host_dst``
+    the bytes are also written there and the host range is registered as resident (the library then
+    owns the device buffer: the returned object will not free it)."""
+    dev = C.c_void_p()
+    got = C.c_int64()
+    _lib.load().dmc_cuda_load_npz(str(path).encode(), key.encode(), rows, cols, wdtype, rank, world,
+                                  0 if host_dst is None else host_dst.ctypes.data, C.byref(dev), C.byref(got))
+    _lib.check()
+    buf = DeviceBuffer.__new__(DeviceBuffer)
+    buf.nbytes = got.value * cols * (2 if wdtype == W_BF16 else 4)
+    buf.ptr = dev.value
+    if host_dst is not None:
+        buf.free = lambda: None          # owned by the registration
+    return buf, got.value
+
+
 def gemv_dev(dW: DeviceBuffer, dx: DeviceBuffer, dy: DeviceBuffer, m: int, k: int, n: int,
              layout: int = LAYOUT_KN, wdtype: int = W_BF16, variant: int = -1) -> None:
     """Asynchronous device-resident GEMV (``dmc_cuda_gemv_dev``)."""

@@ -35,7 +35,8 @@ enum {
     DMC_CUDA_ERR_OOM = 4,         /* device or pinned allocation failed       */
     DMC_CUDA_ERR_NCCL = 5,        /* NCCL missing or a collective failed      */
     DMC_CUDA_ERR_TIMEOUT = 6,     /* a bounded device-side wait ran out       */
-    DMC_CUDA_ERR_UNSUPPORTED = 7  /* shape outside what an entry point takes  */
+    DMC_CUDA_ERR_UNSUPPORTED = 7, /* shape outside what an entry point takes  */
+    DMC_CUDA_ERR_IO = 8           /* a weight file could not be read          */
 };
 
 /* Weight memory layouts. */
@@ -197,6 +198,39 @@ typedef struct dmc_gemv_item {
  * stream; with `use_graph` != 0 the step is captured once into a CUDA graph and
  * replayed.  Returns microseconds per step (< 0 on error). */
 double dmc_cuda_bench_items(const dmc_gemv_item *items, int count, int steps, int warmup, int use_graph);
+
+/* ---- weight ingest ---------------------------------------------------------------------------
+ * Replaces the host side of `vault.load_npz[bf16, [K, N]](path, key = "w")`
+ * (dmc_vault_load_npz, compiler/src/jit.rs:29836-29927: zip entry `<key>.npy` or `<key>`, NPY v1/v2
+ * header, raw little-endian elements) for weights that live on the GPU: the bytes go from the file
+ * through a ring of pinned buffers straight to the device. */
+typedef struct dmc_npz_entry {
+    int64_t data_offset;  /* file offset of the first array byte; -1 when the entry is deflated */
+    int64_t data_bytes;   /* array bytes the entry holds */
+    int64_t shape[4];
+    int ndim;
+    int itemsize;         /* bytes per element, from the header's descr */
+    int fortran_order;
+    int method;           /* 0 stored (numpy.savez), 8 deflated (numpy.savez_compressed) */
+    char descr[16];
+} dmc_npz_entry;
+
+/* Find and describe an entry.  Host only (no device, no context); DMC_CUDA_ERR_IO if the file, the
+ * archive structure, the entry or its NPY header cannot be read. */
+int dmc_npz_locate(const char *path, const char *key, dmc_npz_entry *out);
+
+/* Load the row-major [rows][cols] array of entry `key` (2-byte elements for DMC_W_BF16, 4-byte for
+ * DMC_W_F32), or, with world > 1, only the rows dmc_cuda_shard_range(rows, rank, world) gives this
+ * rank, into a fresh device buffer returned in *dev_out (*rows_out = rows loaded).
+ * host_dst == 0: the caller owns the buffer (dmc_cuda_dev_free).  host_dst != 0: the same bytes are
+ * also written to that host buffer (the Forge allocation the JIT hands around) and the range is
+ * registered as resident, exactly as dmc_cuda_register_weight would, so builtins called with that
+ * host pointer use the device copy; the library then owns the buffer (dmc_cuda_unregister_weight).
+ * Unlike the reference, an entry shorter than rows*cols elements, of another item size or in Fortran
+ * order is an error (DMC_CUDA_ERR_IO), not a partial load.  A deflated entry needs libz.so.1 at run
+ * time.  Synchronous. */
+int dmc_cuda_load_npz(const char *path, const char *key, int64_t rows, int64_t cols, int wdtype, int rank, int world,
+                      int64_t host_dst, void **dev_out, int64_t *rows_out);
 
 /* ---- row-sharded GEMV over the GPUs of one box (one process per GPU) ------------------------
  * No counterpart in the reference, which has no multi-GPU code (its collective names are reserved
