@@ -377,6 +377,7 @@ extern "C" void dmc_cuda_shutdown(void) {
     if (c.d_tmpw) cudaFree(c.d_tmpw);
     if (c.d_tmpx) cudaFree(c.d_tmpx);
     if (c.err_word) cudaFreeHost(c.err_word);
+    if (c.ingest_ring) cudaFreeHost(c.ingest_ring);
     cudaStreamDestroy(c.stream);
     c = Context();
 }
@@ -503,6 +504,7 @@ static int apply_param(const char *name, int64_t value) {
     else if (!strcmp(name, "nk_default")) t.nk_default = (int)value;
     else if (!strcmp(name, "shard_fused")) t.shard_fused = (int)value;
     else if (!strcmp(name, "shard_debug")) t.shard_debug = (int)value;
+    else if (!strcmp(name, "shard_exchange")) t.shard_exchange = (int)value;
     else if (!strcmp(name, "zero_copy_y")) t.zero_copy_y = (int)value;
     else if (!strcmp(name, "decode_fused")) t.decode_fused = (int)value;
     else if (!strcmp(name, "decode_debug")) t.decode_debug = (int)value;

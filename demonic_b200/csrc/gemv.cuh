@@ -377,6 +377,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
     griddep_wait();
     // after the wait: the previous exchange (an earlier kernel) is what advances the epoch word
     const unsigned epoch = a.peer ? peer_epoch(a.peer) : 0u;
+    if (a.peer) peer_begin(a.peer, epoch);
 
     // stage x (after the dependency wait: an earlier kernel may produce it)
     if constexpr (!XG) {

@@ -343,12 +343,13 @@ extern "C" int dmc_cuda_load_npz(const char *path, const char *key, int64_t rows
     auto cleanup = [&](bool keep_dev) {
         for (cudaEvent_t e : ev)
             if (e) cudaEventDestroy(e);
-        if (ring) cudaFreeHost(ring);
         if (dev && !keep_dev) cudaFree(dev);
         close(fd);
     };
     cudaError_t ce = cudaMalloc((void **)&dev, std::max<uint64_t>(total, 16));
-    if (ce == cudaSuccess) ce = cudaMallocHost((void **)&ring, kRingBytes * kRingSlots);
+    // the ring outlives the call: pinning 64 MiB costs as much as reading a few hundred MiB
+    if (ce == cudaSuccess && !c.ingest_ring) ce = cudaMallocHost((void **)&c.ingest_ring, kRingBytes * kRingSlots);
+    ring = c.ingest_ring;
     for (int i = 0; i < kRingSlots && ce == cudaSuccess; ++i) ce = cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming);
     if (ce != cudaSuccess) {
         cleanup(false);

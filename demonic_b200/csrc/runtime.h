@@ -82,6 +82,9 @@ struct Context {
     float *pro_hout = nullptr;
     float pro_eps = 0.0f;
 
+    // pinned staging ring of the weight ingest, allocated on first use
+    unsigned char *ingest_ring = nullptr;
+
     int64_t launches = 0;
 };
 
@@ -103,6 +106,8 @@ struct Tuning {
     int decode_fused = 1;   // decode step: fuse the companions into the GEMVs / attention (0 = one kernel per op)
     int decode_debug = 0;   // measurement only: 1 = skip attention, 2 = skip argmax, 4 = no fused norm on the qkv GEMV
     int shard_debug = 0;
+    int shard_exchange = 3; // fused exchange protocol, read at shard_init: 3 = tagged elements + gather kernel,
+                            // 2 = counted arrivals, 1 = flags by the last CTA
     int shard_fused = -1;   // sharded GEMV: 1 = peer stores fused into the kernel, 0 = NCCL all-gather, -1 = by world size
 };
 

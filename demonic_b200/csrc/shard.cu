@@ -51,12 +51,14 @@ struct Shard {
     void *peer_base[kMaxPeers] = {};  // peers' regions as mapped here (own entry = region)
     PeerOut *d_peer = nullptr;        // device copy of the exchange descriptor
     unsigned *d_epoch = nullptr;
+    int peer_mode = 3;  // 3: tagged elements + gather kernel (default); 2: counted arrivals; 1: flag exchange by the last CTA
     bool fused_ok = false;            // peer mappings are in place
     bool last_fused = false;          // which buffer holds the latest result
 };
 constexpr size_t kTailBytes = 256;
 
-size_t region_bytes(int64_t max_n) { return (size_t)2 * max_n * sizeof(float) + kTailBytes; }
+// [y: 2 * max_n floats][tail: flags, epoch, counters][tagged y: 2 * max_n pairs]
+size_t region_bytes(int64_t max_n) { return (size_t)2 * max_n * sizeof(float) + kTailBytes + (size_t)2 * max_n * 8; }
 
 NcclApi g_nccl;
 Shard g_shard;
@@ -99,25 +101,104 @@ void shard_range(int64_t n, int rank, int world, int64_t *r0, int64_t *r1) {
 }
 
 // Local GEMV into y[r0, r1) then the exchange, all on `s`.
-int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype, cudaStream_t s) {
+// Closes an exchange for consumers that are not themselves a sharded GEMV: returns once every rank's
+// share of the current epoch has been counted here.  One thread.
+__global__ void peer_wait_kernel(const PeerOut *p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x != 0 || (p->debug & 2)) return;
+    const unsigned e = __ldcg(p->epoch);
+    const unsigned target = e * (unsigned)p->world * kPeerQuantum;
+    const unsigned *mine = p->flags[p->rank];
+    const long long t0 = clock64();
+    while ((int)(ld_acquire_sys(mine) - target) < 0) {
+        if (clock64() - t0 > (1LL << 31)) {
+            *(volatile int *)p->err = 5;
+            break;
+        }
+    }
+}
+
+// mode 3: the replicated y arrives as {value, epoch} pairs written by every rank's GEMV; this kernel
+// waits (bounded) until each pair carries the current epoch, writes the plain y, and the CTA that
+// leaves last advances the epoch word.  n: rows of the whole y.
+__global__ void __launch_bounds__(256) peer_gather_kernel(const PeerOut *p, int n) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const unsigned e = __ldcg(p->epoch) + 1u;
+    const unsigned long long *src = p->ty[p->rank] + (size_t)(e & 1u) * p->stride;
+    float *dst = p->yplain;
+    const int pairs2 = n / 2;  // 16-byte pieces
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pairs2; i += gridDim.x * blockDim.x) {
+        unsigned a0, a1, b0, b1;
+        const long long t0 = clock64();
+        for (;;) {
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(b0), "=r"(b1) : "l"(src + 2 * (size_t)i) : "memory");
+            if ((a1 == e && b1 == e) || (p->debug & 2)) break;
+            if (clock64() - t0 > (1LL << 31)) {  // ~1 s: give up instead of hanging
+                *(volatile int *)p->err = 6;
+                break;
+            }
+        }
+        *reinterpret_cast<float2 *>(dst + 2 * (size_t)i) = make_float2(__uint_as_float(a0), __uint_as_float(b0));
+    }
+    if ((n & 1) && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long v;
+        const long long t0 = clock64();
+        for (;;) {
+            asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(src + (n - 1)) : "memory");
+            if ((unsigned)(v >> 32) == e || (p->debug & 2)) break;
+            if (clock64() - t0 > (1LL << 31)) {
+                *(volatile int *)p->err = 6;
+                break;
+            }
+        }
+        dst[n - 1] = __uint_as_float((unsigned)v);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(p->counter, 1u) == gridDim.x - 1u) {
+            *p->counter = 0u;
+            *p->epoch = e;
+            __threadfence();
+        }
+    }
+}
+
+int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype, cudaStream_t s,
+                  bool close_exchange = true) {
     Shard &sh = g_shard;
     if (!sh.ready) return fail(DMC_CUDA_ERR_BAD_ARG, "shard_gemv: dmc_cuda_shard_init has not been called");
     if (n > sh.max_n) return fail(DMC_CUDA_ERR_UNSUPPORTED, "shard_gemv: n=%lld beyond the max_n=%lld given to shard_init",
                                   (long long)n, (long long)sh.max_n);
     int64_t r0, r1;
     shard_range(n, sh.rank, sh.world, &r0, &r1);
-    // Measured on B200 (65536x8192): the fused exchange wins from 4 ranks up (39.3 vs 43.7 us at 8),
-    // ties at 4 and loses to ncclAllGather at 2, where the slices are large and NCCL's copy is cheap.
-    const bool want_fused = tuning().shard_fused < 0 ? sh.world >= 4 : tuning().shard_fused != 0;
+    // Measured on B200 (65536x8192): the fused exchange with epoch-tagged elements is ahead of
+    // ncclAllGather from 2 ranks up (94.3 vs 95.2 us at 2; the older flag exchange had 39.3 vs 43.7 us at 8).
+    const bool want_fused = tuning().shard_fused < 0 ? sh.world >= 2 : tuning().shard_fused != 0;
     if (want_fused && sh.fused_ok && r1 > r0 && k > 0) {
         // one kernel: GEMV whose epilogue stores into every replica and closes with the flag exchange
         Context &c = ctx();
         c.peer = sh.d_peer;
         c.peer_yoff = r0;
+        const int mode = sh.peer_mode;
         int rc = launch_gemv(dW_shard, dx, sh.y + r0, 1, k, r1 - r0, 1, 0, 0, DMC_LAYOUT_NK, wdtype, -1, s);
         c.peer = nullptr;
         c.peer_yoff = 0;
-        sh.last_fused = true;
+        sh.last_fused = mode != 3;  // the gather kernel leaves the plain y in the first buffer
+        if (rc == DMC_CUDA_OK && mode == 3) {
+            const PeerOut *pp = sh.d_peer;
+            int rows = (int)n;
+            void *params[] = {&pp, &rows};
+            const int ctas = (int)std::max<int64_t>(1, std::min<int64_t>(64, (n / 2 + 255) / 256));
+            rc = launch_ex((const void *)peer_gather_kernel, dim3(ctas), dim3(256), 0, s, params);
+        }
+        if (rc == DMC_CUDA_OK && mode == 2 && close_exchange) {
+            const PeerOut *pp = sh.d_peer;
+            void *params[] = {&pp};
+            rc = launch_ex((const void *)peer_wait_kernel, dim3(1), dim3(32), 0, s, params);
+        }
         return rc;
     }
     sh.last_fused = false;
@@ -182,6 +263,7 @@ extern "C" int dmc_cuda_shard_init(int rank, int world, const uint8_t *id128, in
         memcpy(id.internal, id128, 128);
         DMC_NCCL_TRY(g_nccl.CommInitRank(&sh.comm, world, id, rank));
     }
+    max_n = (max_n + 3) & ~(int64_t)3;  // keeps both halves of every double buffer 16-byte aligned
     const size_t bytes = region_bytes(max_n);
     DMC_CUDA_TRY(cudaMalloc((void **)&sh.region, bytes));
     DMC_CUDA_TRY(cudaMemset(sh.region, 0, bytes));
@@ -219,7 +301,9 @@ extern "C" int dmc_cuda_shard_init(int rank, int world, const uint8_t *id128, in
             char *base = static_cast<char *>(sh.peer_base[r]);
             po.y[r] = reinterpret_cast<float *>(base);
             po.flags[r] = reinterpret_cast<unsigned *>(base + (size_t)2 * max_n * sizeof(float));
+            po.ty[r] = reinterpret_cast<unsigned long long *>(base + (size_t)2 * max_n * sizeof(float) + kTailBytes);
         }
+        po.yplain = sh.y;
         unsigned *tail = reinterpret_cast<unsigned *>(sh.region + (size_t)2 * max_n * sizeof(float));
         po.epoch = tail + kMaxPeers;
         po.counter = tail + kMaxPeers + 1;
@@ -228,6 +312,11 @@ extern "C" int dmc_cuda_shard_init(int rank, int world, const uint8_t *id128, in
         po.world = world;
         po.rank = rank;
         po.debug = tuning().shard_debug;
+        // the two fused protocols keep different state in the flag words: the choice is made once, here
+        {
+            const int want = tuning().shard_exchange;
+            po.mode = sh.peer_mode = (want >= 1 && want <= 3) ? want : 3;
+        }
         sh.d_epoch = po.epoch;
         DMC_CUDA_TRY(cudaMalloc((void **)&sh.d_peer, sizeof(PeerOut)));
         DMC_CUDA_TRY(cudaMemcpy(sh.d_peer, &po, sizeof(po), cudaMemcpyHostToDevice));
@@ -287,8 +376,10 @@ extern "C" double dmc_cuda_bench_shard(const void *const *dW_shards, int copies,
     cudaGraphExec_t exec = nullptr;
     double us = -1.0;
     auto one_step = [&]() -> int {
+        // with the counted exchange every GEMV begins by waiting for the previous exchange to have landed,
+        // so only the last one of the step needs the separate closing wait
         for (int i = 0; i < copies; ++i) {
-            int rc = shard_gemv_on(dW_shards[i], dx, k, n, wdtype, s);
+            int rc = shard_gemv_on(dW_shards[i], dx, k, n, wdtype, s, i == copies - 1);
             if (rc) return rc;
         }
         return DMC_CUDA_OK;

@@ -16,13 +16,15 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def test_world_of_one_is_the_plain_gemv():
+@pytest.mark.parametrize("exchange", [3, 2, 1], ids=["tagged", "counted", "flags"])
+def test_world_of_one_is_the_plain_gemv(exchange):
     lib = _lib.load()
     lib.dmc_cuda_clear_error()
     n, k = 3001, 4096                       # odd row count
     rng = np.random.default_rng(41)
     w = synth.bf16_weights(rng, (n, k))
     x = synth.activations(rng, (k,))
+    lib.dmc_cuda_set_param(b"shard_exchange", exchange)      # read when the shard context is created
     sharded.init(0, 1, None, n)
     try:
         dW, dx = backend.DeviceBuffer.from_host(w), backend.DeviceBuffer.from_host(x)
@@ -32,12 +34,13 @@ def test_world_of_one_is_the_plain_gemv():
             sharded.gemv(dW, dx, k, n)
             assert_parity(sharded.output(n), ref, TOL_BF16, f"fused={fused}")
         lib.dmc_cuda_set_param(b"shard_fused", 1)
-        us = sharded.bench([dW], dx, k, n, steps=3, warmup=1)      # graph replays advance the epoch on the device
+        us = sharded.bench([dW, dW, dW], dx, k, n, steps=3, warmup=1)      # graph replays advance the epoch on the device
         assert us > 0
         sharded.gemv(dW, dx, k, n)
         assert_parity(sharded.output(n), ref, TOL_BF16, "after graph replays")
-        lib.dmc_cuda_set_param(b"shard_fused", -1)
     finally:
+        lib.dmc_cuda_set_param(b"shard_fused", -1)
+        lib.dmc_cuda_set_param(b"shard_exchange", 3)
         sharded.shutdown()
     assert lib.dmc_cuda_status() == 0
 
@@ -53,9 +56,11 @@ rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 dist.init_process_group("gloo", rank=rank, world_size=world)
 lib = dmc.load()
 assert lib.dmc_cuda_init(rank) == 0
-ids = [sharded.unique_id() if rank == 0 else None]
-dist.broadcast_object_list(ids, src=0)
-for n in (8192, 1001):                      # even split (all-gather) and ragged split (broadcast group)
+for exchange in (3, 2, 1):                  # tagged elements, counted arrivals, flags by the last CTA
+  lib.dmc_cuda_set_param(b"shard_exchange", exchange)
+  ids = [sharded.unique_id() if rank == 0 else None]
+  dist.broadcast_object_list(ids, src=0)
+  for n in (8192, 1001):                    # even split (all-gather) and ragged split (broadcast group)
     k = 2048
     rng = np.random.default_rng(5)
     w = synth.bf16_weights(rng, (n, k)); x = synth.activations(rng, (k,))
@@ -68,15 +73,16 @@ for n in (8192, 1001):                      # even split (all-gather) and ragged
         sharded.gemv(dW, dx, k, n)
         y = sharded.output(n)
         err = float(np.max(np.abs(y - ref)) / np.max(np.abs(ref)))
-        assert err < 1e-5, (rank, n, fused, err)
+        assert err < 1e-5, (rank, n, exchange, fused, err)
     lib.dmc_cuda_set_param(b"shard_fused", 1)
-    us = sharded.bench([dW], dx, k, n, steps=5, warmup=2)
+    us = sharded.bench([dW, dW, dW], dx, k, n, steps=5, warmup=2)
     sharded.gemv(dW, dx, k, n)
     y = sharded.output(n)
     assert float(np.max(np.abs(y - ref)) / np.max(np.abs(ref))) < 1e-5, "after graph replays"
-    np.save(os.path.join({out!r}, f"y{{rank}}_{{n}}.npy"), y)
-dist.barrier()
-sharded.shutdown()
+    np.save(os.path.join({out!r}, f"y{{rank}}_{{n}}_{{exchange}}.npy"), y)
+  assert lib.dmc_cuda_status() == 0, lib.dmc_cuda_last_error()
+  dist.barrier()
+  sharded.shutdown()
 dist.destroy_process_group()
 """
 
@@ -91,6 +97,7 @@ def test_two_ranks_on_two_gpus(tmp_path):
                            "--master-addr", "127.0.0.1", "--master-port", "29517", str(script)],
                           env=env, capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
-    for n in (8192, 1001):
-        y0, y1 = np.load(tmp_path / f"y0_{n}.npy"), np.load(tmp_path / f"y1_{n}.npy")
-        assert np.array_equal(y0, y1), "the two replicas of y differ"
+    for exchange in (3, 2, 1):
+        for n in (8192, 1001):
+            y0, y1 = np.load(tmp_path / f"y0_{n}_{exchange}.npy"), np.load(tmp_path / f"y1_{n}_{exchange}.npy")
+            assert np.array_equal(y0, y1), "the two replicas of y differ"
