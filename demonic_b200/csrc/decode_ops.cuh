@@ -187,11 +187,28 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float *__restrict
     const int h = blockIdx.x, z = blockIdx.y, splits = gridDim.y;
     const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
     const int t0 = z * chunk;
-    constexpr int KU = 4;
+    constexpr int KU = 8;  // keys in flight per warp: the loop is bound by memory latency, not by arithmetic
     griddep_wait();
     const int pos = *pos_ptr, len = pos + 1;
     const int t1 = min(len, t0 + chunk);
     const bool owns_new = pos >= t0 && pos < t0 + chunk;
+    // The first batch of cached keys/values does not depend on q: request it before the RoPE section, so
+    // the two memory latencies overlap.  (The row at `pos` is the one this launch appends: it is taken
+    // from shared memory below, never from the cache.)
+    float4 k4[KU], v4[KU];
+    auto load_batch = [&](int tb) {
+#pragma unroll
+        for (int u = 0; u < KU; ++u) {
+            const int t = tb + 4 * u;
+            if (t >= t1 || t == pos) {
+                k4[u] = v4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            } else {
+                k4[u] = __ldcg(reinterpret_cast<const float4 *>(kc + ((size_t)h * cap + t) * HD) + lane);
+                v4[u] = __ldcg(reinterpret_cast<const float4 *>(vc + ((size_t)h * cap + t) * HD) + lane);
+            }
+        }
+    };
+    load_batch(t0 + warp);
     {   // RoPE, pairs (2i, 2i+1): thread d holds element d and reads its partner
         const float c = cs[(size_t)pos * (HD / 2) + (d >> 1)], s = sn[(size_t)pos * (HD / 2) + (d >> 1)];
         const float *q = qkv + (size_t)h * HD, *k = qkv + (size_t)(H + h) * HD, *v = qkv + (size_t)(2 * H + h) * HD;
@@ -211,25 +228,16 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float *__restrict
     const float4 q4 = reinterpret_cast<const float4 *>(qs)[lane];
     float m = -INFINITY, l = 0.0f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-    // KU keys in flight per warp: the loop is bound by memory latency, not by arithmetic
     for (int tb = t0 + warp; tb < t1; tb += 4 * KU) {
-        float4 k4[KU], v4[KU];
+        if (tb != t0 + warp) load_batch(tb);
 #pragma unroll
         for (int u = 0; u < KU; ++u) {
             const int t = tb + 4 * u;
-            if (t >= t1) {
-                k4[u] = v4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            } else if (t == pos) {
+            if (t >= t1) break;
+            if (t == pos) {
                 k4[u] = reinterpret_cast<const float4 *>(ks)[lane];
                 v4[u] = reinterpret_cast<const float4 *>(vs)[lane];
-            } else {
-                k4[u] = __ldcg(reinterpret_cast<const float4 *>(kc + ((size_t)h * cap + t) * HD) + lane);
-                v4[u] = __ldcg(reinterpret_cast<const float4 *>(vc + ((size_t)h * cap + t) * HD) + lane);
             }
-        }
-#pragma unroll
-        for (int u = 0; u < KU; ++u) {
-            if (tb + 4 * u >= t1) break;
             float s = q4.x * k4[u].x + q4.y * k4[u].y + q4.z * k4[u].z + q4.w * k4[u].w;
             s = warp_sum(s) * scale;
             const float mn = fmaxf(m, s);
