@@ -156,13 +156,11 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const PeerOut *p, int 
         dst[n - 1] = __uint_as_float((unsigned)v);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(p->counter, 1u) == gridDim.x - 1u) {
-            *p->counter = 0u;
-            *p->epoch = e;
-            __threadfence();
-        }
+    // No fence: the plain y only has to be visible to later kernels, which the end of this one ensures;
+    // the counter merely elects the CTA that advances the epoch.
+    if (threadIdx.x == 0 && atomicAdd(p->counter, 1u) == gridDim.x - 1u) {
+        *p->counter = 0u;
+        *p->epoch = e;
     }
 }
 
@@ -191,7 +189,7 @@ int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, i
             const PeerOut *pp = sh.d_peer;
             int rows = (int)n;
             void *params[] = {&pp, &rows};
-            const int ctas = (int)std::max<int64_t>(1, std::min<int64_t>(64, (n / 2 + 255) / 256));
+            const int ctas = (int)std::max<int64_t>(1, std::min<int64_t>(128, (n / 2 + 255) / 256));  // one 16-byte piece per thread up to 64K rows
             rc = launch_ex((const void *)peer_gather_kernel, dim3(ctas), dim3(256), 0, s, params);
         }
         if (rc == DMC_CUDA_OK && mode == 2 && close_exchange) {
