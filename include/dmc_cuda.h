@@ -295,8 +295,22 @@ void dmc_decoder_destroy(void *dec);
 int dmc_cuda_variant_count(int layout, int wdtype);
 const char *dmc_cuda_variant_name(int layout, int wdtype, int variant);
 
-/* Tuning knobs for sweeps: "pdl" (programmatic dependent launch, default 1),
- * "kn_ctas_per_sm", "kn_ksplit", "nk_ctas_per_sm" (0 = library default). */
+/* Tuning knobs (also read at context creation from the environment variable DMC_CUDA_PARAMS,
+ * "name=value,name=value"); unknown names return DMC_CUDA_ERR_BAD_ARG.
+ *   pdl               1    programmatic dependent launch between the library's kernels
+ *   kn_ctas_per_sm, kn_ksplit, nk_ctas_per_sm            0 = the library's choice per shape
+ *   nk_default        -1   NK kernel configuration used when a call passes variant -1
+ *   tma_ring_kb, tma_stage_kb, tma_ctas_per_sm           shape of the TMA ring kernel (0 = default)
+ *   store_nk          1    keep resident [k, n] weights k-contiguous on the device
+ *   zero_copy_y       1    host-pointer entry points: kernels store y straight into pinned host memory
+ *   tc_min_m          0    activation rows from which `@` goes to the tensor cores (0 = library default)
+ *   tc_ksplit, tc_smem_kb                                tcgen05 GEMM: K splits, shared-memory ring budget
+ *   shard_fused       -1   sharded GEMV: 1 = exchange fused into the kernel, 0 = ncclAllGather, -1 = fused
+ *                          whenever the GPUs have peer access
+ *   shard_exchange    3    protocol of the fused exchange, read by dmc_cuda_shard_init: 3 = epoch-tagged
+ *                          elements + gather kernel, 2 = per-CTA arrival counters, 1 = flags by the last CTA
+ *   decode_fused      1    decode step: companions fused into the GEMVs / attention (0 = one kernel per op)
+ *   shard_debug, decode_debug                            measurement only: leave parts of a step out */
 int dmc_cuda_set_param(const char *name, int64_t value);
 
 /* Kernels this library has launched since the context was created. */
