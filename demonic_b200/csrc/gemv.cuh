@@ -33,6 +33,7 @@ struct GemvArgs {
     long long ls, rs;    // batch strides in elements (x: f32, W: weight elements)
     const PeerOut *peer; // NK kernel, sharded path: store y into every rank's replica (else null)
     long long yoff;      // first row of this rank's slice within the replicated y
+    int peer_j;          // position of this exchange in the current batch of launches
     // NK kernel: an elementwise op applied to x while it is staged into shared memory (0 = none)
     //   1  x = rms_norm(x + add) * g; CTA 0 also stores the sum x + add to hout (the residual stream)
     //   2  x[i] = silu(x[i]) * x[K + i]  (SwiGLU over a [gate | up] vector of 2K floats)
@@ -387,7 +388,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
     if (a.peer) __syncthreads();  // the descriptor copy is complete
     // after the wait: the previous exchange (an earlier kernel) is what advances the epoch word
     const PeerOut *peer = a.peer ? &s_peer : nullptr;
-    const unsigned epoch = peer ? peer_epoch(peer) : 0u;
+    const unsigned epoch = peer ? peer_epoch(peer, a.peer_j) : 0u;
     if (peer) peer_begin(peer, epoch);
 
     // stage x (after the dependency wait: an earlier kernel may produce it)

@@ -351,6 +351,7 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
     int64_t grid = std::max<int64_t>(1, std::min<int64_t>(groups, (int64_t)c.sm_count * cps));
     a.peer = static_cast<const PeerOut *>(c.peer);
     a.yoff = c.peer_yoff;
+    a.peer_j = c.peer_j;
     if (c.pro) {
         if (v.xg || m != 1) return fail(DMC_CUDA_ERR_UNSUPPORTED, "gemv: fused prologue needs the staged kernel and m == 1");
         a.pro = c.pro;

@@ -49,7 +49,12 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
 
 // Epoch this kernel is producing (uniform over the grid: the word only changes in
 // peer_finish of the last CTA, after every CTA has passed its arrival).
-__device__ __forceinline__ unsigned peer_epoch(const PeerOut *p) { return __ldcg(p->epoch) + 1u; }
+// Mode 3 counts differently: the word holds the exchanges completed before the current batch of
+// launches (it is advanced once per batch, by peer_batch_end_kernel) and `j` is the position of this
+// exchange in the batch, so a kernel that does not wait for its predecessor still knows its epoch.
+__device__ __forceinline__ unsigned peer_epoch(const PeerOut *p, int j) {
+    return __ldcg(p->epoch) + 1u + (p->mode == 3 ? (unsigned)j : 0u);
+}
 
 // Each finished output element goes straight into every rank's replica: one local store and
 // world-1 remote stores, issued by the lane that holds the row's sum while the rest of the grid

@@ -75,6 +75,7 @@ struct Context {
     // set by the sharded path around a launch: the NK kernel then stores y into every rank's replica
     const void *peer = nullptr;  // device pointer to a PeerOut
     long long peer_yoff = 0;
+    int peer_j = 0;
 
     // set by the decode step around a launch: elementwise prologue of the NK kernel's x staging
     int pro = 0;

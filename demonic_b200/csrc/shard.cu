@@ -119,26 +119,44 @@ __global__ void peer_wait_kernel(const PeerOut *p) {
     }
 }
 
-// mode 3: the replicated y arrives as {value, epoch} pairs written by every rank's GEMV; this kernel
-// waits (bounded) until each pair carries the current epoch, writes the plain y, and the CTA that
-// leaves last advances the epoch word.  n: rows of the whole y.
-__global__ void __launch_bounds__(256) peer_gather_kernel(const PeerOut *p, int n) {
+// mode 3: the replicated y arrives as {value, epoch} pairs written by every rank's GEMV.  This kernel
+// does not wait for the local GEMV to complete (whose completion includes the acknowledgement of its
+// remote stores): it runs beside it, and re-reads each pair (bounded) until it carries the epoch of
+// this exchange, then writes the plain y of that epoch's parity.  j: position of the exchange in the
+// current batch of launches; n: rows of the whole y.
+__global__ void __launch_bounds__(256) peer_gather_kernel(const PeerOut *p, int n, int j) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const unsigned e = __ldcg(p->epoch) + 1u;
+    // the epoch word was advanced before any kernel of this batch could start (peer_batch_end_kernel)
+    const unsigned e = *(volatile const unsigned *)p->epoch + 1u + (unsigned)j;
     const unsigned long long *src = p->ty[p->rank] + (size_t)(e & 1u) * p->stride;
-    float *dst = p->yplain;
+    float *dst = p->yplain + (size_t)(e & 1u) * p->stride;
     const int pairs2 = n / 2;  // 16-byte pieces
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pairs2; i += gridDim.x * blockDim.x) {
+    const bool skip = (p->debug & 2) != 0;
+    const int first = blockIdx.x * blockDim.x;
+    // While the GEMVs are still streaming, one thread per CTA watches one piece at a relaxed pace, so
+    // that the 32K threads of this grid do not load L2 for the whole duration of the GEMV.
+    if (threadIdx.x == 0 && first < pairs2 && !skip) {
+        const long long t0 = clock64();
+        for (;;) {
+            unsigned a0, a1, b0, b1;
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(b0), "=r"(b1) : "l"(src + 2 * (size_t)first) : "memory");
+            if (a1 == e && b1 == e) break;
+            if (clock64() - t0 > (1LL << 31)) break;  // the loop below reports it
+            __nanosleep(200);
+        }
+    }
+    __syncthreads();
+    for (int i = first + threadIdx.x; i < pairs2; i += gridDim.x * blockDim.x) {
         unsigned a0, a1, b0, b1;
         const long long t0 = clock64();
         for (;;) {
             asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(b0), "=r"(b1) : "l"(src + 2 * (size_t)i) : "memory");
-            if ((a1 == e && b1 == e) || (p->debug & 2)) break;
+            if ((a1 == e && b1 == e) || skip) break;
             if (clock64() - t0 > (1LL << 31)) {  // ~1 s: give up instead of hanging
                 *(volatile int *)p->err = 6;
                 break;
             }
+            __nanosleep(100);
         }
         *reinterpret_cast<float2 *>(dst + 2 * (size_t)i) = make_float2(__uint_as_float(a0), __uint_as_float(b0));
     }
@@ -147,25 +165,33 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const PeerOut *p, int 
         const long long t0 = clock64();
         for (;;) {
             asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(src + (n - 1)) : "memory");
-            if ((unsigned)(v >> 32) == e || (p->debug & 2)) break;
+            if ((unsigned)(v >> 32) == e || skip) break;
             if (clock64() - t0 > (1LL << 31)) {
                 *(volatile int *)p->err = 6;
                 break;
             }
+            __nanosleep(100);
         }
         dst[n - 1] = __uint_as_float((unsigned)v);
     }
-    __syncthreads();
-    // No fence: the plain y only has to be visible to later kernels, which the end of this one ensures;
-    // the counter merely elects the CTA that advances the epoch.
-    if (threadIdx.x == 0 && atomicAdd(p->counter, 1u) == gridDim.x - 1u) {
-        *p->counter = 0u;
-        *p->epoch = e;
-    }
 }
 
+// mode 3: closes a batch of `count` exchanges.  Waits for everything before it, then advances the
+// epoch word -- before any kernel of the next batch can start, since those launch only after the
+// launch_dependents below.
+__global__ void peer_batch_end_kernel(const PeerOut *p, int count) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) {
+        *(volatile unsigned *)p->epoch = *(volatile unsigned *)p->epoch + (unsigned)count;
+        __threadfence();
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// j: position of this call in a batch of back-to-back sharded GEMVs; end_batch: it is the last one.
 int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype, cudaStream_t s,
-                  bool close_exchange = true) {
+                  int j = 0, bool end_batch = true) {
     Shard &sh = g_shard;
     if (!sh.ready) return fail(DMC_CUDA_ERR_BAD_ARG, "shard_gemv: dmc_cuda_shard_init has not been called");
     if (n > sh.max_n) return fail(DMC_CUDA_ERR_UNSUPPORTED, "shard_gemv: n=%lld beyond the max_n=%lld given to shard_init",
@@ -180,19 +206,26 @@ int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, i
         Context &c = ctx();
         c.peer = sh.d_peer;
         c.peer_yoff = r0;
+        c.peer_j = j;
         const int mode = sh.peer_mode;
         int rc = launch_gemv(dW_shard, dx, sh.y + r0, 1, k, r1 - r0, 1, 0, 0, DMC_LAYOUT_NK, wdtype, -1, s);
         c.peer = nullptr;
         c.peer_yoff = 0;
-        sh.last_fused = mode != 3;  // the gather kernel leaves the plain y in the first buffer
+        c.peer_j = 0;
+        sh.last_fused = true;
         if (rc == DMC_CUDA_OK && mode == 3) {
             const PeerOut *pp = sh.d_peer;
-            int rows = (int)n;
-            void *params[] = {&pp, &rows};
+            int rows = (int)n, jj = j;
+            void *params[] = {&pp, &rows, &jj};
             const int ctas = (int)std::max<int64_t>(1, std::min<int64_t>(128, (n / 2 + 255) / 256));  // one 16-byte piece per thread up to 64K rows
             rc = launch_ex((const void *)peer_gather_kernel, dim3(ctas), dim3(256), 0, s, params);
+            if (rc == DMC_CUDA_OK && end_batch) {
+                int count = j + 1;
+                void *params2[] = {&pp, &count};
+                rc = launch_ex((const void *)peer_batch_end_kernel, dim3(1), dim3(32), 0, s, params2);
+            }
         }
-        if (rc == DMC_CUDA_OK && mode == 2 && close_exchange) {
+        if (rc == DMC_CUDA_OK && mode == 2 && end_batch) {
             const PeerOut *pp = sh.d_peer;
             void *params[] = {&pp};
             rc = launch_ex((const void *)peer_wait_kernel, dim3(1), dim3(32), 0, s, params);
@@ -346,7 +379,8 @@ extern "C" float *dmc_cuda_shard_output(void) {
     Shard &sh = g_shard;
     if (!sh.ready) return nullptr;
     if (!sh.last_fused) return sh.y;
-    // the fused exchange alternates between two buffers; the epoch word says which one is current
+    // the fused exchange alternates between two buffers; after a synchronisation the epoch word counts the
+    // completed exchanges, so its parity names the current one
     unsigned e = 0;
     cudaStreamSynchronize(ctx().stream);
     cudaMemcpy(&e, sh.d_epoch, sizeof(e), cudaMemcpyDeviceToHost);
@@ -377,7 +411,7 @@ extern "C" double dmc_cuda_bench_shard(const void *const *dW_shards, int copies,
         // with the counted exchange every GEMV begins by waiting for the previous exchange to have landed,
         // so only the last one of the step needs the separate closing wait
         for (int i = 0; i < copies; ++i) {
-            int rc = shard_gemv_on(dW_shards[i], dx, k, n, wdtype, s, i == copies - 1);
+            int rc = shard_gemv_on(dW_shards[i], dx, k, n, wdtype, s, i, i == copies - 1);
             if (rc) return rc;
         }
         return DMC_CUDA_OK;
