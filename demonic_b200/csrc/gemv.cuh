@@ -476,17 +476,22 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
             consume(c);
         }
         first = false;
+        float mine = 0.0f;  // sharded path: lane j keeps the sum of row j
 #pragma unroll
         for (int j = 0; j < R; ++j) {
             float s = acc[j];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);  // every lane ends with the sum
             const int row = row0 + j;
-            if (lane == 0 && row < rend) {
-                if (peer) peer_store(peer, epoch, a.yoff + row, s);
-                else a.y[row] = s;
+            if (peer) {
+                if (lane == j) mine = s;
+            } else if (lane == 0 && row < rend) {
+                a.y[row] = s;
             }
         }
+        // The R rows of a warp are adjacent, so lanes 0..R-1 store them together: one R*8-byte write per
+        // replica instead of R separate ones (fewer, larger NVLink packets).
+        if (peer && lane < R && row0 + lane < rend) peer_store(peer, epoch, a.yoff + row0 + lane, mine);
     }
     if (peer) peer_finish<THREADS>(peer, epoch, &s_last);
 }
