@@ -66,10 +66,17 @@ class ClockSampler:
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
-            time.sleep(0.25)
+            t0 = time.time()
+            while not self.lines and time.time() - t0 < 5.0:      # nvidia-smi is up and sampling
+                time.sleep(0.02)
         except OSError:
             self.proc = None
+        self.before = len(self.lines)
         return self
+
+    def samples_under_load(self) -> int:
+        """Samples taken since the timed region began."""
+        return len(self.lines) - self.before
 
     def _read(self):
         for line in self.proc.stdout:
@@ -87,7 +94,7 @@ class ClockSampler:
     def summary(self) -> dict:
         sm, mx, reasons = [], 0.0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for ln in self.lines[getattr(self, "before", 0):] or self.lines:
             f = [t.strip() for t in ln.split(",")]
             if len(f) < 7:
                 continue
@@ -231,6 +238,11 @@ def run_single(args) -> None:
     with ClockSampler() as clocks:
         us_step = backend.bench_items(step_items, args.steps, args.warmup, use_graph=True)
         backend.sync()
+        # a short timed region can fall between two samples: keep the same load running, untimed,
+        # until the sampler has seen it a few times
+        t_tail = time.time()
+        while clocks.samples_under_load() < 3 and time.time() - t_tail < 2.0:
+            backend.bench_items(step_items, args.steps, 0, use_graph=True)
     launches_total = lib.dmc_cuda_launch_count() - launches0
     # bench_items runs 1 eager sizing step + 1 captured step + warmup + K timed replays
     per_step = len(step_items)

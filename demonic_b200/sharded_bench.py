@@ -85,8 +85,12 @@ def run(args, rank: int, world: int) -> None:
     with bench_mod.ClockSampler(local) as clocks:
         us = sharded.bench(bufs, dx, COLS, ROWS, args.steps, args.warmup, use_graph=True)
         backend.sync()
+        launches_timed_run = lib.dmc_cuda_launch_count() - launches0
+        # the timed region lasts a few milliseconds: the same load, untimed, keeps running for ~0.3 s so
+        # that the clock samples are taken under it (every rank runs the same number of exchanges)
+        sharded.bench(bufs, dx, COLS, ROWS, max(1, int(3e5 / max(us, 1.0))), 0, use_graph=True)
+        backend.sync()
     # dmc_cuda_bench_shard runs 1 eager step + 1 captured step + warmup + K timed replays
-    launches_timed_run = lib.dmc_cuda_launch_count() - launches0
     launches_per_step = launches_timed_run // (2 + args.warmup + args.steps)
     dist.barrier()
     t = [us]
