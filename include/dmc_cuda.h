@@ -249,8 +249,12 @@ int dmc_cuda_shard_init(int rank, int world, const uint8_t *id128, int64_t max_n
 void dmc_cuda_shard_shutdown(void);
 
 /* y = W.x for W[n][k] (k contiguous) of which this rank holds rows dmc_cuda_shard_range(n, rank, world)
- * in `dW_shard` (device).  Runs the local GEMV, then all-gathers the f32 slices so every rank holds
- * the whole y in dmc_cuda_shard_output().  Asynchronous on the context's stream; collective. */
+ * in `dW_shard` (device).  Runs the local GEMV and exchanges the f32 slices so that every rank holds
+ * the whole y in dmc_cuda_shard_output(): between GPUs with peer access the GEMV kernel itself stores
+ * its rows into every rank's replica over NVLink (each element tagged with the number of the exchange,
+ * validated by a small kernel running beside it); otherwise, or with "shard_fused" = 0, ncclAllGather
+ * follows the kernel.  Asynchronous on the context's stream; collective (every rank calls it, in the
+ * same order); dx must not alias dmc_cuda_shard_output() of the call before the previous one. */
 int dmc_cuda_shard_gemv(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype);
 float *dmc_cuda_shard_output(void);
 
