@@ -161,7 +161,7 @@ def run_reference(args, shapes, workload: str, rank: int, world: int) -> None:
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
-        "vs_baseline": None, "dtype": "f32 accumulate over bf16 weights", "data": "synthetic",
+        "vs_baseline": None, "dtype": "f32", "weights": "bf16 (widened exactly, f32 FMA accumulate)", "data": "synthetic",
         "config": {"workload": workload, "timed": "one pass of the CPU kernel over the workload per step"},
         "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "host_cores": os.cpu_count(),
                          "sample": f"{args.steps} passes over the workload; dmc_matmul_bf16 order and thread policy "
@@ -307,7 +307,7 @@ def run_single(args) -> None:
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": us_step / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32 accumulate over bf16 weights", "data": "synthetic",
+        "dtype": "f32", "weights": "bf16 (widened exactly, f32 FMA accumulate)", "data": "synthetic",
         "config": {"workload": "batch-1 decode-shape bf16 GEMV sweep (BASELINE config 2), y = W.x, W [rows, cols] k-contiguous",
                    "shapes": [f"{r}x{c}" for r, c in SWEEP], "gemvs_per_step": per_step,
                    "l2": f"inputs larger than L2: each shape rotates over >= {ROTATE_BYTES >> 20} MiB of distinct weight copies",

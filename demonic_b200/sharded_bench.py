@@ -133,7 +133,7 @@ def run(args, rank: int, world: int) -> None:
         line = {
             "metric": bench_mod.METRIC, "value": value, "unit": bench_mod.UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": us_max / 1e3, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32 accumulate over bf16 weights", "data": "synthetic",
+            "vs_baseline": None, "dtype": "f32", "weights": "bf16 (widened exactly, f32 FMA accumulate)", "data": "synthetic",
             "config": {"workload": f"row-sharded bf16 GEMV {ROWS}x{COLS} (BASELINE config 5), rows split evenly over "
                                    f"{world} GPUs, output slices exchanged into a replicated y: "
                                    + EXCHANGE_TEXT[chosen],
