@@ -86,17 +86,17 @@ def run(args, rank: int, world: int) -> None:
         us = sharded.bench(bufs, dx, COLS, ROWS, args.steps, args.warmup, use_graph=True)
         backend.sync()
         launches_timed_run = lib.dmc_cuda_launch_count() - launches0
-        # the timed region lasts a few milliseconds: the same load, untimed, keeps running for ~0.3 s so
-        # that the clock samples are taken under it (every rank runs the same number of exchanges)
-        sharded.bench(bufs, dx, COLS, ROWS, max(1, int(3e5 / max(us, 1.0))), 0, use_graph=True)
+        allt = [None] * world
+        dist.all_gather_object(allt, [us])
+        us_max = max(v[0] for v in allt)
+        # The timed region lasts a few milliseconds: the same load, untimed, keeps running for ~0.3 s so
+        # that the clock samples are taken under it.  The exchange is collective: every rank must run the
+        # same number of steps, hence the count comes from the maximum over ranks, not from its own time.
+        sharded.bench(bufs, dx, COLS, ROWS, max(1, int(3e5 / max(us_max, 1.0))), 0, use_graph=True)
         backend.sync()
     # dmc_cuda_bench_shard runs 1 eager step + 1 captured step + warmup + K timed replays
     launches_per_step = launches_timed_run // (2 + args.warmup + args.steps)
     dist.barrier()
-    t = [us]
-    allt = [None] * world
-    dist.all_gather_object(allt, t)
-    us_max = max(v[0] for v in allt)
     # the same step with each exchange forced: fused into the kernel (peer stores + flags) and ncclAllGather
     forced = {}
     for name, mode in (("fused_peer_stores", 1), ("nccl_allgather", 0)):
