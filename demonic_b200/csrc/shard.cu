@@ -199,7 +199,7 @@ int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, i
     int64_t r0, r1;
     shard_range(n, sh.rank, sh.world, &r0, &r1);
     // Measured on B200 (65536x8192): the fused exchange is ahead of ncclAllGather from 2 ranks up
-    // (92.0 vs 95.5 us at 2, 26.0 vs 42.5 us at 8).
+    // (89.5 vs 95.4 us at 2, 26.0 vs 42.5 us at 8).
     const bool want_fused = tuning().shard_fused < 0 ? sh.world >= 2 : tuning().shard_fused != 0;
     if (want_fused && sh.fused_ok && r1 > r0 && k > 0) {
         // one kernel: GEMV whose epilogue stores into every replica and closes with the flag exchange
