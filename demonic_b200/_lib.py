@@ -29,7 +29,7 @@ SIGNATURES = {
     "dmc_matmul_f32_gpu": (None, [I64] * 6),
     "dmc_matmul_bf16_gpu_nt": (None, [I64] * 6),
     "dmc_cuda_matmul_selected": (C.c_int, [C.c_int, C.c_uint32, I64, I64, I64, I64, C.c_int]),
-    "dmc_cuda_register_weight": (C.c_int, [I64, I64, C.c_int]),
+    "dmc_cuda_register_weight": (C.c_int, [I64, I64, I64, I64, C.c_int, C.c_int]),
     "dmc_cuda_unregister_weight": (C.c_int, [I64]),
     "dmc_cuda_resident_count": (I64, []),
     "dmc_cuda_resident_bytes": (I64, []),
@@ -48,6 +48,10 @@ SIGNATURES = {
     "dmc_cuda_shard_shutdown": (None, []),
     "dmc_cuda_shard_gemv": (C.c_int, [VP, VP, I64, I64, C.c_int]),
     "dmc_cuda_shard_output": (VP, []),
+    "dmc_cuda_shard_output_previous": (VP, []),
+    "dmc_cuda_shard_uses_fused": (C.c_int, [I64, I64]),
+    "dmc_cuda_shard_probe_timeout": (C.c_int, [I64]),
+    "dmc_cuda_shard_path": (C.c_int, [C.c_int, C.c_int, C.c_int, I64, I64]),
     "dmc_cuda_bench_shard": (C.c_double, [VP, C.c_int, VP, I64, I64, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_gemm_dev": (C.c_int, [VP, VP, VP, I64, I64, I64, C.c_int]),
     "dmc_decoder_create": (C.c_int, [VP, C.POINTER(VP)]),
@@ -77,7 +81,8 @@ class NpzEntry(C.Structure):
 class GemvItem(C.Structure):
     """``dmc_gemv_item`` of include/dmc_cuda.h."""
     _fields_ = [("W", VP), ("x", VP), ("y", VP), ("m", I64), ("k", I64), ("n", I64),
-                ("layout", C.c_int), ("wdtype", C.c_int), ("variant", C.c_int), ("op", C.c_int)]
+                ("layout", C.c_int), ("wdtype", C.c_int), ("variant", C.c_int), ("op", C.c_int),
+                ("batch", I64), ("ls", I64), ("rs", I64)]
 
 
 

@@ -157,15 +157,19 @@ def gemv_dev(dW: DeviceBuffer, dx: DeviceBuffer, dy: DeviceBuffer, m: int, k: in
 
 def bench_items(items: list[tuple], steps: int, warmup: int = 3, use_graph: bool = True) -> float:
     """Device-timed microseconds per step (``dmc_cuda_bench_items``).  Each item is
-    ``(dW, dx, dy, m, k, n, layout, wdtype, variant[, op])`` with DeviceBuffers; ``op`` 0 (default)
-    is the GEMV path, 1 / 2 the tensor-core GEMM with bf16 / f32 activations."""
+    ``(dW, dx, dy, m, k, n, layout, wdtype, variant[, op[, (batch, ls, rs)]])``; ``dW`` / ``dx`` / ``dy``
+    are DeviceBuffers or ``(DeviceBuffer, byte offset)`` pairs; ``op`` 0 (default) is the GEMV path,
+    1 / 2 the tensor-core GEMM with bf16 / f32 activations."""
+    def addr(b):
+        return b[0].ptr + b[1] if isinstance(b, tuple) else b.ptr
     arr = (_lib.GemvItem * len(items))()
     for slot, item in zip(arr, items):
         dW, dx, dy, m, k, n, layout, wdtype, variant = item[:9]
-        slot.W, slot.x, slot.y = dW.ptr, dx.ptr, dy.ptr
+        slot.W, slot.x, slot.y = addr(dW), addr(dx), addr(dy)
         slot.m, slot.k, slot.n = m, k, n
         slot.layout, slot.wdtype, slot.variant = layout, wdtype, variant
         slot.op = item[9] if len(item) > 9 else 0
+        slot.batch, slot.ls, slot.rs = item[10] if len(item) > 10 else (1, 0, 0)
     us = _lib.load().dmc_cuda_bench_items(C.cast(arr, C.c_void_p), len(items), steps, warmup, int(use_graph))
     _lib.check()
     return float(us)

@@ -41,7 +41,7 @@ struct Decoder {
 
 template <typename T>
 int dalloc(T **p, size_t count) {
-    DMC_CUDA_TRY(cudaMalloc((void **)p, count * sizeof(T)));
+    DMC_CUDA_TRY(dmc_malloc((void **)p, count * sizeof(T)));
     DMC_CUDA_TRY(cudaMemset(*p, 0, count * sizeof(T)));
     return DMC_CUDA_OK;
 }
@@ -81,9 +81,8 @@ int enqueue_step_fused(Decoder &d, cudaStream_t s) {
     for (int l = 0; l < c.layers; ++l) {
         Layer &L = d.layers[l];
         // qkv = Wqkv . rms_norm(h + carry);  h' = h + carry
-        if ((rc = gemv_pro(L.wqkv, hin, d.qkv, D, 3 * D, (tuning().decode_debug & 4) ? 0 : 1, carry, L.g1, hout, c.eps, s))) return rc;
+        if ((rc = gemv_pro(L.wqkv, hin, d.qkv, D, 3 * D, 1, carry, L.g1, hout, c.eps, s))) return rc;
         std::swap(hin, hout);
-        if (!(tuning().decode_debug & 1))
         if ((rc = launch_small(attn_fused_kernel, dim3(H, d.splits), dim3(128), s, (const float *)d.qkv,
                                (const float *)d.rope_cos, (const float *)d.rope_sin, L.kc, L.vc, d.part, d.ao, d.attn_cnt, H,
                                cap, (const int *)d.d_pos, chunk)))
@@ -97,7 +96,6 @@ int enqueue_step_fused(Decoder &d, cudaStream_t s) {
         carry = d.d2;
     }
     if ((rc = gemv_pro(d.lm_head, hin, d.logits, D, V, 1, carry, d.gf, nullptr, c.eps, s))) return rc;
-    if (tuning().decode_debug & 2) return DMC_CUDA_OK;
     return launch_small(argmax_kernel, dim3(64), dim3(256), s, (const float *)d.logits, V, d.d_next, d.am_val, d.am_idx, d.am_cnt);
 }
 

@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <ctime>
 
 #include "runtime.h"
 
@@ -35,6 +36,31 @@ int fail(int code, const char *fmt, ...) {
         if (getenv("DMC_CUDA_DEBUG")) fprintf(stderr, "[dmc_cuda] error %d: %s\n", code, g_msg);
     }
     return code;
+}
+
+// Host-side failure injection for tests: DMC_CUDA_INJECT is a comma-separated list of the calls
+// that should report failure without being made ("malloc", "malloc_host", "nccl_init", "ipc_open",
+// "stream").  Nothing on the device is touched by an injected failure.
+bool inject_failure(const char *what) {
+    const char *env = getenv("DMC_CUDA_INJECT");
+    if (!env || !*env) return false;
+    const size_t n = strlen(what);
+    for (const char *p = env; *p;) {
+        const char *q = strchr(p, ',');
+        const size_t len = q ? (size_t)(q - p) : strlen(p);
+        if (len == n && !strncmp(p, what, n)) return true;
+        if (!q) break;
+        p = q + 1;
+    }
+    return false;
+}
+cudaError_t dmc_malloc(void **p, size_t bytes) {
+    if (inject_failure("malloc")) return cudaErrorMemoryAllocation;
+    return cudaMalloc(p, bytes);
+}
+cudaError_t dmc_malloc_host(void **p, size_t bytes) {
+    if (inject_failure("malloc_host")) return cudaErrorMemoryAllocation;
+    return cudaMallocHost(p, bytes);
 }
 
 // Content fingerprint of a weight buffer: byte length plus a 256-point strided
@@ -84,10 +110,13 @@ static int init_locked(int device) {
                     device, prop.major, prop.minor);
     c.device = device;
     c.sm_count = prop.multiProcessorCount;
+    c.clock_khz = prop.clockRate > 0 ? prop.clockRate : 1900000;
+    if (inject_failure("stream")) return fail(DMC_CUDA_ERR_CUDA, "cudaStreamCreateWithFlags failed: injected");
     DMC_CUDA_TRY(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
-    DMC_CUDA_TRY(cudaMallocHost((void **)&c.err_word, sizeof(int)));
+    DMC_CUDA_TRY(dmc_malloc_host((void **)&c.err_word, sizeof(int)));
     *c.err_word = 0;
     apply_env_params();
+    if (getenv("DMC_CUDA_TIME") && atoi(getenv("DMC_CUDA_TIME")) != 0) g_tuning.timing = 1;
     c.ready = true;
     return DMC_CUDA_OK;
 }
@@ -114,6 +143,17 @@ int ensure_init() {
 
 // ---- staging ---------------------------------------------------------------------
 
+// Wait for the stream.  The host-pointer builtins are latency-bound (a 10 us kernel between two
+// small copies), and a blocking synchronise adds a thread wake-up to every call: "spin_sync" polls
+// the stream instead, at the price of a busy host core while the GPU works.
+static cudaError_t stream_wait(cudaStream_t s) {
+    if (!g_tuning.spin_sync) return cudaStreamSynchronize(s);
+    for (;;) {
+        cudaError_t e = cudaStreamQuery(s);
+        if (e != cudaErrorNotReady) return e;
+    }
+}
+
 static int flush_locked();
 
 static int grow_pair(char **h, char **d, size_t *cap, size_t need) {
@@ -128,8 +168,8 @@ static int grow_pair(char **h, char **d, size_t *cap, size_t need) {
     *h = nullptr;
     *d = nullptr;
     *cap = 0;
-    DMC_CUDA_TRY(cudaMallocHost((void **)h, ncap));
-    DMC_CUDA_TRY(cudaMalloc((void **)d, ncap));
+    DMC_CUDA_TRY(dmc_malloc_host((void **)h, ncap));
+    DMC_CUDA_TRY(dmc_malloc((void **)d, ncap));
     *cap = ncap;
     return DMC_CUDA_OK;
 }
@@ -148,7 +188,8 @@ static int flush_locked() {
     Context &c = g_ctx;
     if (!c.ready) return g_status;
     if (c.pending.empty() && c.x_off == 0 && c.y_off == 0) return g_status;
-    DMC_CUDA_TRY(cudaStreamSynchronize(c.stream));
+    DMC_CUDA_TRY(stream_wait(c.stream));
+    stream_drained();
     if (check_device_error()) {  // results of a kernel that gave up are not delivered
         c.pending.clear();
         c.x_off = c.y_off = 0;
@@ -163,8 +204,40 @@ static int flush_locked() {
 
 // ---- resident weights ---------------------------------------------------------------
 
-// Find or create the device copy of a host weight.  A single [k, n] bf16 matrix that
-// the TMA kernel can take is stored transposed ([n, k], k contiguous) so the one
+// Copy a host weight to a fresh device buffer; with `transposed` the [k, n] matrix is stored
+// [n, k] (k contiguous) by one device transpose.  Synchronous.
+static int upload_weight(uintptr_t r, size_t bytes, int64_t k, int64_t n, size_t wsz, bool transposed, void **out) {
+    Context &c = g_ctx;
+    void *d = nullptr;
+    DMC_CUDA_TRY(dmc_malloc(&d, bytes ? bytes : 16));
+    void *staging = d;
+    if (transposed) {
+        cudaError_t e = dmc_malloc(&staging, bytes);
+        if (e != cudaSuccess) {
+            cudaFree(d);
+            return fail(DMC_CUDA_ERR_OOM, "weight upload: staging allocation failed: %s", cudaGetErrorString(e));
+        }
+    }
+    // On the context's stream, not the legacy default stream: a plain cudaMemcpy from pageable memory
+    // may return before its DMA lands, and the non-blocking stream would not wait for it.
+    cudaError_t e = cudaMemcpyAsync(staging, (const void *)r, bytes, cudaMemcpyHostToDevice, c.stream);
+    if (e == cudaSuccess && !transposed) e = cudaStreamSynchronize(c.stream);
+    if (e == cudaSuccess && transposed) {
+        int rc = launch_transpose(staging, d, k, n, (int)wsz, c.stream);
+        e = rc ? cudaErrorUnknown : cudaStreamSynchronize(c.stream);  // the GEMV may prefetch W before its dependency wait
+        cudaFree(staging);
+    }
+    if (e != cudaSuccess) {
+        cudaFree(d);
+        return fail(DMC_CUDA_ERR_CUDA, "weight upload failed: %s", cudaGetErrorString(e));
+    }
+    stream_drained();
+    *out = d;
+    return DMC_CUDA_OK;
+}
+
+// Find or create the device copy of a host weight.  A single [k, n] matrix that the
+// row-streaming kernel can take is stored transposed ([n, k], k contiguous) so the one
 // bandwidth kernel serves it; *layout says how the returned buffer is laid out.
 // The transpose runs once per weight, on the device, at upload.
 static int resident_weight(uintptr_t r, size_t bytes, int64_t k, int64_t n, int wdtype, bool may_transpose,
@@ -173,8 +246,16 @@ static int resident_weight(uintptr_t r, size_t bytes, int64_t k, int64_t n, int 
     *layout = DMC_LAYOUT_KN;
     for (const RegisteredRange &rg : c.registered) {
         if (r >= rg.host && r + bytes <= rg.host + rg.bytes) {
-            *dev = (char *)rg.dev + (r - rg.host);
-            return DMC_CUDA_OK;
+            if (rg.k == 0) {  // stored as the host has it
+                *dev = (char *)rg.dev + (r - rg.host);
+                return DMC_CUDA_OK;
+            }
+            if (may_transpose && r == rg.host && bytes == rg.bytes && k == rg.k && n == rg.n) {
+                *dev = rg.dev;
+                *layout = DMC_LAYOUT_NK;
+                return DMC_CUDA_OK;
+            }
+            break;  // a different view of a range stored k-contiguous: served by content below
         }
     }
     const size_t wsz = wdtype == DMC_W_BF16 ? 2 : 4;
@@ -195,28 +276,8 @@ static int resident_weight(uintptr_t r, size_t bytes, int64_t k, int64_t n, int 
         for (const RegisteredRange &rg : c.registered) c.resident_bytes += (int64_t)rg.bytes;
     }
     void *d = nullptr;
-    DMC_CUDA_TRY(cudaMalloc(&d, bytes ? bytes : 16));
-    void *staging = d;
-    if (transposed) {
-        cudaError_t e = cudaMalloc(&staging, bytes);
-        if (e != cudaSuccess) {
-            cudaFree(d);
-            return fail(DMC_CUDA_ERR_OOM, "weight upload: staging allocation failed: %s", cudaGetErrorString(e));
-        }
-    }
-    // On the context's stream, not the legacy default stream: a plain cudaMemcpy from pageable memory
-    // may return before its DMA lands, and the non-blocking stream would not wait for it.
-    cudaError_t e = cudaMemcpyAsync(staging, (const void *)r, bytes, cudaMemcpyHostToDevice, c.stream);
-    if (e == cudaSuccess && !transposed) e = cudaStreamSynchronize(c.stream);
-    if (e == cudaSuccess && transposed) {
-        int rc = launch_transpose(staging, d, k, n, (int)wsz, c.stream);
-        e = rc ? cudaErrorUnknown : cudaStreamSynchronize(c.stream);  // the GEMV may prefetch W before its dependency wait
-        cudaFree(staging);
-    }
-    if (e != cudaSuccess) {
-        cudaFree(d);
-        return fail(DMC_CUDA_ERR_CUDA, "weight upload failed: %s", cudaGetErrorString(e));
-    }
+    int rc = upload_weight(r, bytes, k, n, wsz, transposed, &d);
+    if (rc) return rc;
     if (getenv("DMC_CUDA_DEBUG"))
         fprintf(stderr, "[dmc_cuda] upload #%zu %zu MB%s\n", c.by_fingerprint.size() + 1, bytes >> 20,
                 transposed ? " (stored k-contiguous)" : "");
@@ -239,8 +300,13 @@ struct HostCall {
     bool resident;  // keep r on the device across calls
 };
 
-static int run_host_call(const HostCall &h) {
-    std::lock_guard<std::mutex> lock(g_mutex);
+static double now_us() {
+    timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return ts.tv_sec * 1e6 + ts.tv_nsec * 1e-3;
+}
+
+static int run_host_call_locked(const HostCall &h) {
     if (g_status) return g_status;  // sticky: nothing runs after a failure
     if (h.m < 0 || h.k < 0 || h.n < 0 || h.batch < 0 || h.ls < 0 || h.rs < 0)
         return fail(DMC_CUDA_ERR_BAD_ARG, "matmul: negative size (m=%lld k=%lld n=%lld batch=%lld ls=%lld rs=%lld)",
@@ -248,8 +314,23 @@ static int run_host_call(const HostCall &h) {
                     (long long)h.rs);
     if (h.m == 0 || h.n == 0 || h.batch == 0) return DMC_CUDA_OK;  // compiler/src/gpu.rs:402, 425
     if (!h.l || !h.r || !h.out) return fail(DMC_CUDA_ERR_BAD_ARG, "matmul: null operand pointer");
-    if (h.batch > 1 && h.m != 1)
-        return fail(DMC_CUDA_ERR_UNSUPPORTED, "batched matmul takes m == 1 slices (got m=%lld)", (long long)h.m);
+    if (h.batch > 1 && h.m != 1) {
+        // The JIT only batches m == 1 slices; for anything else the reference runs the slices one
+        // after the other (compiler/src/gpu.rs:428-437), and so does this -- on the GPU.
+        for (int64_t z = 0; z < h.batch; ++z) {
+            HostCall one = h;
+            one.l = h.l + z * h.ls;
+            one.r = (const char *)h.r + (size_t)z * h.rs * (h.wdtype == DMC_W_BF16 ? 2 : 4);
+            one.out = h.out + z * h.m * h.n;
+            one.batch = 1;
+            one.ls = one.rs = 0;
+            int rc = run_host_call_locked(one);
+            if (rc) return rc;
+        }
+        return DMC_CUDA_OK;
+    }
+    const bool timing = g_tuning.timing != 0;
+    const double t0 = timing ? now_us() : 0.0;
     int rc = ensure_init();
     if (rc) return rc;
     Context &c = g_ctx;
@@ -296,16 +377,24 @@ static int run_host_call(const HostCall &h) {
             bool hit = false;
             for (const RegisteredRange &rg : c.registered)
                 if ((uintptr_t)h.r >= rg.host && (uintptr_t)h.r + w_elems * wsz <= rg.host + rg.bytes) {
-                    dW = (char *)rg.dev + ((uintptr_t)h.r - rg.host);
-                    hit = true;
+                    if (rg.k == 0) {
+                        dW = (char *)rg.dev + ((uintptr_t)h.r - rg.host);
+                        hit = true;
+                    } else if ((uintptr_t)h.r == rg.host && w_elems * wsz == rg.bytes && h.k == rg.k && h.n == rg.n &&
+                               h.batch == 1 && h.layout == DMC_LAYOUT_KN) {
+                        dW = rg.dev;
+                        layout = DMC_LAYOUT_NK;
+                        hit = true;
+                    }
                 }
             if (!hit) {
                 if (w_elems * wsz > c.tmpw_cap) {
                     DMC_CUDA_TRY(cudaStreamSynchronize(c.stream));
+                    stream_drained();
                     if (c.d_tmpw) cudaFree(c.d_tmpw);
                     c.d_tmpw = nullptr;
                     c.tmpw_cap = 0;
-                    DMC_CUDA_TRY(cudaMalloc((void **)&c.d_tmpw, w_elems * wsz));
+                    DMC_CUDA_TRY(dmc_malloc((void **)&c.d_tmpw, w_elems * wsz));
                     c.tmpw_cap = w_elems * wsz;
                 }
                 // pageable source: the copy returns once the source has been consumed
@@ -314,6 +403,7 @@ static int run_host_call(const HostCall &h) {
             }
         }
     }
+    const double t1 = timing ? now_us() : 0.0;
 
     memcpy(c.h_x + x_base, h.l, x_elems * 4);
     DMC_CUDA_TRY(cudaMemcpyAsync(c.d_x + x_base, c.h_x + x_base, x_elems * 4, cudaMemcpyHostToDevice, c.stream));
@@ -322,20 +412,51 @@ static int run_host_call(const HostCall &h) {
     // launch latency on every call; "zero_copy_y" = 0 goes through the device buffer and a copy.
     const bool zc = g_tuning.zero_copy_y != 0;
     float *y_target = zc ? (float *)(c.h_y + y_base) : (float *)(c.d_y + y_base);
+    if (timing) {
+        if (!c.ev0) {
+            DMC_CUDA_TRY(cudaEventCreate(&c.ev0));
+            DMC_CUDA_TRY(cudaEventCreate(&c.ev1));
+        }
+        DMC_CUDA_TRY(cudaEventRecord(c.ev0, c.stream));
+    }
     rc = launch_gemv(dW, (const float *)(c.d_x + x_base), y_target, h.m, h.k, h.n, h.batch,
                      h.ls, h.rs, layout, h.wdtype, -1, c.stream);
     if (rc) return rc;
+    if (timing) DMC_CUDA_TRY(cudaEventRecord(c.ev1, c.stream));
     if (!zc) DMC_CUDA_TRY(cudaMemcpyAsync(c.h_y + y_base, c.d_y + y_base, y_elems * 4, cudaMemcpyDeviceToHost, c.stream));
+    const double t2 = timing ? now_us() : 0.0;
 
+    c.pending.push_back(PendingReadback{(const float *)(c.h_y + y_base), h.out, y_elems});
+    c.x_off = x_base + x_elems * 4;  // (also makes the flush below non-trivial when nothing was deferred)
     if (h.defer) {
-        c.pending.push_back(PendingReadback{(const float *)(c.h_y + y_base), h.out, y_elems});
-        c.x_off = x_base + x_elems * 4;
         c.y_off = y_base + y_elems * 4;
+        if (timing)
+            fprintf(stderr, "[dmc_cuda time] deferred m=%lld k=%lld n=%lld batch=%lld: weights %.1f us, stage+launch %.1f us\n",
+                    (long long)h.m, (long long)h.k, (long long)h.n, (long long)h.batch, t1 - t0, t2 - t1);
         return DMC_CUDA_OK;
     }
-    c.pending.push_back(PendingReadback{(const float *)(c.h_y + y_base), h.out, y_elems});
-    c.x_off = x_base + x_elems * 4;  // make the flush below non-trivial even with nothing deferred
-    return flush_locked();
+    if (!timing) return flush_locked();
+    // the flush, taken apart: wait for the stream, then the host copies of every pending output
+    const size_t npending = c.pending.size();
+    cudaError_t we = stream_wait(c.stream);
+    const double t3 = now_us();
+    if (we != cudaSuccess) return fail(DMC_CUDA_ERR_CUDA, "stream wait failed: %s", cudaGetErrorString(we));
+    rc = flush_locked();
+    const double t4 = now_us();
+    float kms = 0.0f;
+    cudaEventElapsedTime(&kms, c.ev0, c.ev1);
+    const double bytes = (double)w_elems * wsz + 4.0 * x_elems + 4.0 * y_elems;
+    fprintf(stderr,
+            "[dmc_cuda time] m=%lld k=%lld n=%lld batch=%lld %s: weights %.1f us, stage+launch %.1f us, wait %.1f us, "
+            "readback %.1f us (%zu outputs), total %.1f us; kernel %.1f us = %.0f GB/s\n",
+            (long long)h.m, (long long)h.k, (long long)h.n, (long long)h.batch, layout == DMC_LAYOUT_NK ? "k-contiguous" : "n-contiguous",
+            t1 - t0, t2 - t1, t3 - t2, t4 - t3, npending, t4 - t0, kms * 1e3, kms > 0 ? bytes / (kms * 1e-3) / 1e9 : 0.0);
+    return rc;
+}
+
+static int run_host_call(const HostCall &h) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    return run_host_call_locked(h);
 }
 
 }  // namespace dmc
@@ -378,6 +499,8 @@ extern "C" void dmc_cuda_shutdown(void) {
     if (c.d_tmpx) cudaFree(c.d_tmpx);
     if (c.err_word) cudaFreeHost(c.err_word);
     if (c.ingest_ring) cudaFreeHost(c.ingest_ring);
+    if (c.ev0) cudaEventDestroy(c.ev0);
+    if (c.ev1) cudaEventDestroy(c.ev1);
     cudaStreamDestroy(c.stream);
     c = Context();
 }
@@ -430,29 +553,35 @@ extern "C" int dmc_cuda_matmul_selected(int flag_on, uint32_t deterministic_dept
     const __int128 macs1 = (__int128)m * k * n;
     if (!rhs_bf16) return macs1 >= ((__int128)1 << 17);
     if (batch == 1) return (__int128)k * n >= 4000000;
-    return batch <= 65536 && macs1 * batch >= 1000000;
+    // batched projections: m == 1 slices of a width the vector kernels take (compiler/src/jit.rs:19912-19915)
+    return m == 1 && n % 4 == 0 && batch <= 65536 && macs1 * batch >= 1000000;
 }
 
-extern "C" int dmc_cuda_register_weight(int64_t ptr, int64_t bytes, int wdtype) {
+extern "C" int dmc_cuda_register_weight(int64_t ptr, int64_t bytes, int64_t k, int64_t n, int layout, int wdtype) {
     std::lock_guard<std::mutex> lock(ctx_mutex());
     if (dmc::status()) return dmc::status();
     if (!ptr || bytes <= 0 || (wdtype != DMC_W_BF16 && wdtype != DMC_W_F32))
         return fail(DMC_CUDA_ERR_BAD_ARG, "register_weight: bad range or type");
+    const size_t wsz = wdtype == DMC_W_BF16 ? 2 : 4;
+    const bool shaped = k > 0 && n > 0;
+    if (shaped && ((layout != DMC_LAYOUT_KN && layout != DMC_LAYOUT_NK) || (__int128)k * n * (int64_t)wsz != bytes))
+        return fail(DMC_CUDA_ERR_BAD_ARG, "register_weight: %lld bytes is not a [%lld, %lld] matrix of %zu-byte elements",
+                    (long long)bytes, (long long)k, (long long)n, wsz);
     int rc = ensure_init();
     if (rc) return rc;
     Context &c = ctx();
     for (const RegisteredRange &rg : c.registered)
         if ((uintptr_t)ptr < rg.host + rg.bytes && rg.host < (uintptr_t)ptr + (size_t)bytes)
             return fail(DMC_CUDA_ERR_BAD_ARG, "register_weight: range overlaps a registered range");
+    // A [k, n] matrix (the operand of `x @ w`) is stored k-contiguous, like a weight found by its
+    // fingerprint, so that the row-streaming kernel serves it; every other range is kept as it is.
+    const bool transposed = shaped && layout == DMC_LAYOUT_KN && tuning().store_nk && nk_fast_eligible(k, n, wdtype);
     void *d = nullptr;
-    DMC_CUDA_TRY(cudaMalloc(&d, (size_t)bytes));
-    cudaError_t e = cudaMemcpyAsync(d, (const void *)ptr, (size_t)bytes, cudaMemcpyHostToDevice, c.stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(c.stream);
-    if (e != cudaSuccess) {
-        cudaFree(d);
-        return fail(DMC_CUDA_ERR_CUDA, "register_weight: upload failed: %s", cudaGetErrorString(e));
-    }
-    c.registered.push_back(RegisteredRange{(uintptr_t)ptr, (size_t)bytes, d, wdtype});
+    rc = upload_weight((uintptr_t)ptr, (size_t)bytes, k, n, wsz, transposed, &d);
+    if (rc) return rc;
+    RegisteredRange rg{(uintptr_t)ptr, (size_t)bytes, d, wdtype};
+    if (transposed) rg.k = k, rg.n = n;
+    c.registered.push_back(rg);
     c.resident_bytes += bytes;
     return DMC_CUDA_OK;
 }
@@ -503,11 +632,12 @@ static int apply_param(const char *name, int64_t value) {
     else if (!strcmp(name, "store_nk")) t.store_nk = (int)value;
     else if (!strcmp(name, "nk_default")) t.nk_default = (int)value;
     else if (!strcmp(name, "shard_fused")) t.shard_fused = (int)value;
-    else if (!strcmp(name, "shard_debug")) t.shard_debug = (int)value;
-    else if (!strcmp(name, "shard_exchange")) t.shard_exchange = (int)value;
+    else if (!strcmp(name, "overlap_independent")) t.overlap_independent = (int)value;
+    else if (!strcmp(name, "wait_limit_us")) t.wait_limit_us = (int)value;
+    else if (!strcmp(name, "timing")) t.timing = (int)value;
+    else if (!strcmp(name, "spin_sync")) t.spin_sync = (int)value;
     else if (!strcmp(name, "zero_copy_y")) t.zero_copy_y = (int)value;
     else if (!strcmp(name, "decode_fused")) t.decode_fused = (int)value;
-    else if (!strcmp(name, "decode_debug")) t.decode_debug = (int)value;
     else if (!strcmp(name, "tc_ksplit")) t.tc_ksplit = (int)value;
     else if (!strcmp(name, "tc_smem_kb")) t.tc_smem_kb = (int)value;
     else if (!strcmp(name, "tc_min_m")) t.tc_min_m = (int)value;
@@ -544,7 +674,7 @@ extern "C" void *dmc_cuda_dev_alloc(int64_t bytes) {
     std::lock_guard<std::mutex> lock(ctx_mutex());
     if (dmc::status() || ensure_init()) return nullptr;
     void *p = nullptr;
-    cudaError_t e = cudaMalloc(&p, bytes > 0 ? (size_t)bytes : 16);
+    cudaError_t e = dmc_malloc(&p, bytes > 0 ? (size_t)bytes : 16);
     if (e != cudaSuccess) {
         fail(DMC_CUDA_ERR_OOM, "dev_alloc(%lld) failed: %s", (long long)bytes, cudaGetErrorString(e));
         return nullptr;
@@ -559,6 +689,7 @@ extern "C" int dmc_cuda_h2d(void *dst, const void *src, int64_t bytes) {
     if (dmc::status()) return dmc::status();
     DMC_CUDA_TRY(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, ctx().stream));
     DMC_CUDA_TRY(cudaStreamSynchronize(ctx().stream));
+    stream_drained();
     return DMC_CUDA_OK;
 }
 extern "C" int dmc_cuda_d2h(void *dst, const void *src, int64_t bytes) {
@@ -566,6 +697,7 @@ extern "C" int dmc_cuda_d2h(void *dst, const void *src, int64_t bytes) {
     if (dmc::status()) return dmc::status();
     DMC_CUDA_TRY(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToHost, ctx().stream));
     DMC_CUDA_TRY(cudaStreamSynchronize(ctx().stream));
+    stream_drained();
     return DMC_CUDA_OK;
 }
 extern "C" int dmc_cuda_memset(void *dst, int value, int64_t bytes) {
@@ -578,6 +710,7 @@ extern "C" int dmc_cuda_sync(void) {
     std::lock_guard<std::mutex> lock(ctx_mutex());
     if (!ctx().ready) return dmc::status();
     DMC_CUDA_TRY(cudaStreamSynchronize(ctx().stream));
+    stream_drained();
     return check_device_error();
 }
 
@@ -629,7 +762,8 @@ extern "C" double dmc_cuda_bench_items(const dmc_gemv_item *items, int count, in
             int rc;
             if (it.op == 1) rc = launch_gemm_tc(it.W, it.x, it.y, it.m, it.k, it.n, 0, s);
             else if (it.op == 2) rc = launch_gemm_tc_f32x(it.W, it.x, it.y, it.m, it.k, it.n, s);
-            else rc = launch_gemv(it.W, it.x, it.y, it.m, it.k, it.n, 1, 0, 0, it.layout, it.wdtype, it.variant, s);
+            else rc = launch_gemv(it.W, it.x, it.y, it.m, it.k, it.n, it.batch > 1 ? it.batch : 1, it.batch > 1 ? it.ls : 0,
+                                  it.batch > 1 ? it.rs : 0, it.layout, it.wdtype, it.variant, s);
             if (rc) return rc;
         }
         return DMC_CUDA_OK;
@@ -639,6 +773,7 @@ extern "C" double dmc_cuda_bench_items(const dmc_gemv_item *items, int count, in
         int rc = one_step();
         if (rc) return rc;
         DMC_CUDA_TRY(cudaStreamSynchronize(s));
+        stream_drained();
         DMC_CUDA_TRY(cudaEventCreate(&e0));
         DMC_CUDA_TRY(cudaEventCreate(&e1));
         int64_t per_step = 0;
@@ -647,6 +782,7 @@ extern "C" double dmc_cuda_bench_items(const dmc_gemv_item *items, int count, in
             DMC_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
             rc = one_step();
             cudaError_t ce = cudaStreamEndCapture(s, &graph);
+            stream_drained();  // a graph launch is ordered after everything before it in the stream
             if (rc) return rc;
             DMC_CUDA_TRY(ce);
             per_step = c.launches - before;

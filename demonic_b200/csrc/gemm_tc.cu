@@ -39,8 +39,8 @@ int make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t cols, int
 
 using TcFn = void (*)(const CUtensorMap, const CUtensorMap, const GemmTcArgs);
 struct TcEntry { int nb; TcFn fn; };
-const TcEntry kTc[] = {{16, gemm_tc_kernel<16>}, {32, gemm_tc_kernel<32>}, {64, gemm_tc_kernel<64>},
-                       {128, gemm_tc_kernel<128>}, {256, gemm_tc_kernel<256>}};
+const TcEntry kTc[] = {{16, dmc_tc_contract_kernel<16>}, {32, dmc_tc_contract_kernel<32>}, {64, dmc_tc_contract_kernel<64>},
+                       {128, dmc_tc_contract_kernel<128>}, {256, dmc_tc_contract_kernel<256>}};
 
 }  // namespace
 
@@ -119,12 +119,12 @@ int launch_gemm_tc_f32x(const void *dW, const float *dX, float *dY, int64_t m, i
         if (c.d_tmpx) cudaFree(c.d_tmpx);
         c.d_tmpx = nullptr;
         c.tmpx_cap = 0;
-        DMC_CUDA_TRY(cudaMalloc((void **)&c.d_tmpx, need));
+        DMC_CUDA_TRY(dmc_malloc((void **)&c.d_tmpx, need));
         c.tmpx_cap = need;
     }
     const long long total = (long long)m * k;
     const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)c.sm_count * 8);
-    split_x_kernel<<<blocks, 256, 0, stream>>>(dX, (uint16_t *)c.d_tmpx, (int)m, (int)k);
+    dmc_split_x_kernel<<<blocks, 256, 0, stream>>>(dX, (uint16_t *)c.d_tmpx, (int)m, (int)k);
     DMC_CUDA_TRY(cudaGetLastError());
     c.launches++;
     return launch_gemm_tc(dW, c.d_tmpx, dY, m, k, n, 1, stream);

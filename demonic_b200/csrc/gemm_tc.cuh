@@ -40,7 +40,7 @@ struct GemmTcArgs {
 
 template <int NB>
 __global__ void __launch_bounds__(192, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+dmc_tc_contract_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const GemmTcArgs a) {
     constexpr int XTILE = NB * kTcBK * 2;
     constexpr int STAGE = kTcWTileBytes + XTILE;
@@ -220,7 +220,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
 // f32 activations -> (hi, lo) bf16 row pairs, so the tensor cores see x to 16 mantissa bits:
 // row 2j = bf16(x_j) and row 2j+1 = bf16(x_j - hi), both round-to-nearest-even.
-__global__ void __launch_bounds__(256) split_x_kernel(const float *__restrict__ x, uint16_t *__restrict__ xs, int m,
+__global__ void __launch_bounds__(256) dmc_split_x_kernel(const float *__restrict__ x, uint16_t *__restrict__ xs, int m,
                                                       int k) {
     const long long total = (long long)m * k;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {

@@ -8,7 +8,7 @@
 // Weights are bf16 bit patterns (widen = bits << 16, compiler/src/jit.rs:29224-29227)
 // or f32; activations and outputs are f32; accumulation is f32 FMA.  The
 // summation order differs from the reference's ascending-k chain (split across
-// warps / CTAs), which the reference allows for its own GPU path
+// lanes / warps / CTAs), which the reference allows for its own GPU path
 // ("within f32 reduction-order tolerance", compiler/src/gpu.rs:35-37).
 //
 // Every weight byte is read exactly once with 128-bit streaming loads that
@@ -31,6 +31,10 @@ struct GemvArgs {
     int kchunk, ksplit;  // KN: rows of k per CTA along grid.y
     int colblocks;       // KN: CTAs along n per batch slice
     long long ls, rs;    // batch strides in elements (x: f32, W: weight elements)
+    // NK kernel: 1 = nothing this launch reads or writes is touched by a kernel that may still be
+    // running, so the programmatic-dependency wait is skipped and the launch overlaps its
+    // predecessors freely (set by the launch planner, never by a caller)
+    int nowait;
     const PeerOut *peer; // NK kernel, sharded path: store y into every rank's replica (else null)
     long long yoff;      // first row of this rank's slice within the replicated y
     int peer_j;          // position of this exchange in the current batch of launches
@@ -88,6 +92,18 @@ __device__ __forceinline__ void axpy_vec(float *acc, const uint4 &w, float xv) {
     }
 }
 
+// The EPV elements of one 16-byte weight vector, widened to f32.
+template <typename WT>
+__device__ __forceinline__ void widen_vec(const uint4 &w, float (&f)[8]) {
+    if constexpr (sizeof(WT) == 2) {
+        f[0] = bf16lo(w.x), f[1] = bf16hi(w.x), f[2] = bf16lo(w.y), f[3] = bf16hi(w.y);
+        f[4] = bf16lo(w.z), f[5] = bf16hi(w.z), f[6] = bf16lo(w.w), f[7] = bf16hi(w.w);
+    } else {
+        f[0] = __uint_as_float(w.x), f[1] = __uint_as_float(w.y), f[2] = __uint_as_float(w.z), f[3] = __uint_as_float(w.w);
+        f[4] = f[5] = f[6] = f[7] = 0.0f;
+    }
+}
+
 // acc += dot(w[0..EPV), x[0..EPV)) (NK layout); xa holds x[0..4), xb x[4..8).
 template <typename WT>
 __device__ __forceinline__ float dot_vec(float acc, const uint4 &w, const float4 &xa, const float4 &xb) {
@@ -109,9 +125,9 @@ __device__ __forceinline__ float dot_vec(float acc, const uint4 &w, const float4
     return acc;
 }
 
-// Split-K epilogue shared by both layouts: the CTA that arrives last at the
-// group's counter adds the partials in a fixed order (so results do not vary
-// from run to run), writes y and re-arms the counter for the next launch.
+// Split-K epilogue: the CTA that arrives last at the group's counter adds the
+// partials in a fixed order (so results do not vary from run to run), writes y
+// and re-arms the counter for the next launch.
 //   partial index: ((z*ksplit + j)*M + m)*N + col
 template <int THREADS>
 __device__ __forceinline__ void splitk_finish(const GemvArgs &a, int z, int group, int M, int col0,
@@ -147,7 +163,7 @@ __device__ __forceinline__ void splitk_finish(const GemvArgs &a, int z, int grou
 // grid.x = colblocks * batch, grid.y = ksplit.  Needs N % EPV == 0, rs % EPV == 0
 // and a 16-byte aligned W.
 template <int TK, int U, int V, int M, typename WT>
-__global__ void __launch_bounds__(TK * 32) gemv_kn_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(TK * 32) dmc_wcols_kernel(const GemvArgs a) {
     constexpr int EPV = VecOf<WT>::EPV;
     constexpr int CW = 32 * V * EPV;
     constexpr int THREADS = TK * 32;
@@ -160,7 +176,7 @@ __global__ void __launch_bounds__(TK * 32) gemv_kn_kernel(const GemvArgs a) {
     const WT *Wz = (const WT *)a.W + (size_t)z * a.rs;
     const float *xz = a.x + (size_t)z * a.ls;
     const int kbeg = blockIdx.y * a.kchunk;
-    const int kend = min(K, kbeg + a.kchunk);
+    const int kend = (int)min((long long)K, (long long)kbeg + a.kchunk);  // 64-bit: kbeg + kchunk may pass 2^31
 
     int col[V];
     bool cok[V];
@@ -250,7 +266,7 @@ __global__ void __launch_bounds__(TK * 32) gemv_kn_kernel(const GemvArgs a) {
 // kernel; it exists so no shape ever leaves the GPU.  Reference analogue:
 // `gemv_bf16_tiled2d`, compiler/src/gpu.rs:158-183.
 template <int TK, typename WT>
-__global__ void __launch_bounds__(TK * 32) gemv_kn_generic_kernel(const GemvArgs a, int M) {
+__global__ void __launch_bounds__(TK * 32) dmc_wcols_any_kernel(const GemvArgs a, int M) {
     __shared__ float red[TK][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int cb = blockIdx.x % a.colblocks, z = blockIdx.x / a.colblocks;
@@ -284,32 +300,34 @@ __global__ void __launch_bounds__(TK * 32) gemv_kn_generic_kernel(const GemvArgs
 
 // ---- NK layout ----------------------------------------------------------------
 //
-// x is staged once per CTA in shared memory (permuted so a lane's two float4
-// reads are conflict-free); each warp owns R rows at a time and streams them
-// with U 16-byte loads in flight per row (2 KB*U/4 contiguous per row per
-// step), then reduces across lanes with shuffles.  CTAs stride over row groups.
-// Needs K % EPV == 0 and a 16-byte aligned W.  Dynamic shared memory: K floats
-// rounded up to a multiple of 256.
-// XG = true reads x straight from global memory (L1-cached, after the dependency wait) instead of
-// staging it in shared memory: no prologue copy, no barrier, no shared memory.
-// PF > 0 additionally requests the next PF chunks of a warp's first row group with cp.async into
-// shared memory before the dependency wait (the first chunk is already in registers), so that for
-// short rows the whole matrix is in flight while the previous kernel is still running.
-template <int WARPS, int R, int U, typename WT, bool XG = false, int PF = 0>
-__global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
+// The M rows of x (M = 1 for a GEMV; 2, 4 or 8 for a small batch, which shares
+// every weight load among its rows) are staged once per CTA in shared memory,
+// each row permuted so that a lane's two float4 reads are conflict-free.  A CTA
+// owns a contiguous block of row groups (R adjacent weight rows each) and deals
+// them to its warps; a warp streams a group with U 16-byte loads in flight per
+// row, keeps R*M accumulators and reduces across lanes with shuffles.  The grid
+// is either one group per warp (when that fits in one wave) or exactly
+// SMs x resident CTAs, every CTA with the same share of the rows.
+// Needs K % EPV == 0 and a 16-byte aligned W.  Dynamic shared memory: M rows of
+// K floats, each rounded up to a multiple of 256 floats.
+template <int WARPS, int R, int U, int M, typename WT>
+__global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a) {
     constexpr int EPV = VecOf<WT>::EPV;
     constexpr int THREADS = WARPS * 32;
+    constexpr int NACC = M == 1 ? 2 : 1;  // a single row keeps two accumulator chains per weight row
     extern __shared__ __align__(16) float xs[];
     float4 *xs4 = reinterpret_cast<float4 *>(xs);
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int K = a.K, N = a.N;
     const int nvec = K / EPV;
+    const int xrow4 = (K + 255) / 256 * 64;  // float4 slots per staged row of x
     const uint4 *W4 = reinterpret_cast<const uint4 *>(a.W);
 
-    // groups of R rows are dealt round-robin over all warps of the grid
-    const int rend = N;
-    const int rstride = (int)gridDim.x * WARPS * R;
+    // this CTA's block of row groups
+    const int groups = (N + R - 1) / R;
+    const int g0 = (int)(((long long)groups * blockIdx.x) / gridDim.x);
+    const int g1 = (int)(((long long)groups * (blockIdx.x + 1)) / gridDim.x);
 
     uint4 w[R][U];
     auto load_w = [&](int row0, int c) {
@@ -319,91 +337,98 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int cc = c + 32 * u;
-                w[j][u] = (row < rend && cc < nvec) ? ldg_stream16(W4 + (size_t)row * nvec + cc)
-                                                    : make_uint4(0, 0, 0, 0);
+                w[j][u] = (row < N && cc < nvec) ? ldg_stream16(W4 + (size_t)row * nvec + cc)
+                                                 : make_uint4(0, 0, 0, 0);
             }
         }
     };
-    float acc[R];
+    float acc[R][M][NACC];
     auto consume = [&](int c) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int cc = c + 32 * u;
-            float4 xa = make_float4(0, 0, 0, 0), xb = xa;
-            if (cc < nvec) {
-                if constexpr (XG) {
-                    const float4 *xg = reinterpret_cast<const float4 *>(a.x) + (size_t)cc * (EPV / 4);
-                    xa = xg[0];
-                    if constexpr (EPV == 8) xb = xg[1];
-                } else if constexpr (EPV == 8) {
-                    // block of 32 vectors = 64 float4: low halves first, then high halves
-                    const int blk = cc >> 5, l = cc & 31;
-                    xa = xs4[blk * 64 + l];
-                    xb = xs4[blk * 64 + 32 + l];
-                } else {
-                    xa = xs4[cc];
+            if constexpr (M == 1) {
+                float4 xa = make_float4(0, 0, 0, 0), xb = xa;
+                if (cc < nvec) {
+                    if constexpr (EPV == 8) {
+                        // block of 32 vectors = 64 float4: low halves first, then high halves
+                        const int blk = cc >> 5, l = cc & 31;
+                        xa = xs4[blk * 64 + l];
+                        xb = xs4[blk * 64 + 32 + l];
+                    } else {
+                        xa = xs4[cc];
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < R; ++j) acc[j][0][u & 1] = dot_vec<WT>(acc[j][0][u & 1], w[j][u], xa, xb);
+            } else {
+                // several rows of x: widen each weight vector once, reuse it for every row
+                float wf[R][8];
+#pragma unroll
+                for (int j = 0; j < R; ++j) widen_vec<WT>(w[j][u], wf[j]);
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    float4 xa = make_float4(0, 0, 0, 0), xb = xa;
+                    if (cc < nvec) {
+                        if constexpr (EPV == 8) {
+                            const int blk = cc >> 5, l = cc & 31;
+                            xa = xs4[m * xrow4 + blk * 64 + l];
+                            xb = xs4[m * xrow4 + blk * 64 + 32 + l];
+                        } else {
+                            xa = xs4[m * xrow4 + cc];
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < R; ++j) {
+                        float s = acc[j][m][0];
+                        s = fmaf(xa.x, wf[j][0], s);
+                        s = fmaf(xa.y, wf[j][1], s);
+                        s = fmaf(xa.z, wf[j][2], s);
+                        s = fmaf(xa.w, wf[j][3], s);
+                        if constexpr (EPV == 8) {
+                            s = fmaf(xb.x, wf[j][4], s);
+                            s = fmaf(xb.y, wf[j][5], s);
+                            s = fmaf(xb.z, wf[j][6], s);
+                            s = fmaf(xb.w, wf[j][7], s);
+                        }
+                        acc[j][m][0] = s;
+                    }
                 }
             }
-#pragma unroll
-            for (int j = 0; j < R; ++j) acc[j] = dot_vec<WT>(acc[j], w[j][u], xa, xb);
         }
     };
 
-    __shared__ int s_last;
-    int row0 = ((int)blockIdx.x * WARPS + warp) * R;
-    if (row0 < rend) load_w(row0, lane);
-    // prefetch area: [warp][chunk 1..PF][R][U][lane] 16-byte slots after the x staging area
-    uint4 *pf = nullptr;
-    if constexpr (PF > 0) {
-        const size_t xs_bytes = XG ? 0 : (size_t)((K + 255) / 256 * 256) * sizeof(float);
-        pf = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(xs) + xs_bytes) + (size_t)warp * (PF * R * U * 32);
-        if (row0 < rend) {
-#pragma unroll
-            for (int p = 0; p < PF; ++p)
-#pragma unroll
-                for (int j = 0; j < R; ++j)
-#pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        const int cc = lane + (p + 1) * 32 * U + 32 * u, row = row0 + j;
-                        if (row < rend && cc < nvec)
-                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(
-                                             &pf[((p * R + j) * U + u) * 32 + lane])),
-                                         "l"(W4 + (size_t)row * nvec + cc)
-                                         : "memory");
-                    }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    }
+    griddep_launch_dependents();
+    int g = g0 + warp;
+    if (g < g1) load_w(g * R, lane);  // weights depend on no earlier kernel: first loads go out before the wait
     // The exchange descriptor is copied into shared memory once per CTA: read through the global
     // pointer, every field would have to be reloaded after each output store (the compiler cannot
-    // rule out that a store hits the descriptor), which cost ~0.6 us per row group.
+    // rule out that a store hits the descriptor).
     __shared__ PeerOut s_peer;
     static_assert(sizeof(PeerOut) % 4 == 0, "PeerOut is copied word by word");
     if (a.peer) {
         for (int i = threadIdx.x; i < (int)(sizeof(PeerOut) / 4); i += THREADS)
             reinterpret_cast<unsigned *>(&s_peer)[i] = __ldg(reinterpret_cast<const unsigned *>(a.peer) + i);
     }
-    griddep_launch_dependents();
-    griddep_wait();
-    if (a.peer) __syncthreads();  // the descriptor copy is complete
-    // after the wait: the previous exchange (an earlier kernel) is what advances the epoch word
+    if (!a.nowait) griddep_wait();
+    // after the wait: an earlier kernel (the end of the previous batch) is what advances the epoch word
     const PeerOut *peer = a.peer ? &s_peer : nullptr;
+    if (a.peer) __syncthreads();  // the descriptor copy is complete
     const unsigned epoch = peer ? peer_epoch(peer, a.peer_j) : 0u;
-    if (peer) peer_begin(peer, epoch);
 
     // stage x (after the dependency wait: an earlier kernel may produce it)
-    if constexpr (!XG) {
-        const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
+    {
         const int n4 = K / 4;
-        auto slot = [&](int i) -> float4 & {
+        auto slot = [&](int m, int i) -> float4 & {
             if constexpr (EPV == 8) {
                 const int blk = i >> 6, idx = i & 63;
-                return xs4[blk * 64 + (idx & 1) * 32 + (idx >> 1)];
+                return xs4[m * xrow4 + blk * 64 + (idx & 1) * 32 + (idx >> 1)];
             } else {
-                return xs4[i];
+                return xs4[m * xrow4 + i];
             }
         };
-        if (a.pro == 1) {
+        const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
+        if (M == 1 && a.pro == 1) {
             // RMSNorm of the residual stream fused into the staging (f32 form of the JIT,
             // compiler/src/jit.rs:23776-23847): every CTA normalises its own copy of x
             __shared__ float red[WARPS];
@@ -418,7 +443,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
                 }
                 if (h4 && blockIdx.x == 0) h4[i] = v;
                 ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
-                slot(i) = v;
+                slot(0, i) = v;
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -430,75 +455,70 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_nk_kernel(const GemvArgs a) {
             const float inv = 1.0f / sqrtf(tot / (float)K + a.pro_eps);
             const float4 *g4 = reinterpret_cast<const float4 *>(a.pro_g);
             for (int i = threadIdx.x; i < n4; i += THREADS) {  // each thread rescales what it stored itself
-                float4 v = slot(i);
-                const float4 g = __ldg(g4 + i);
-                v.x = v.x * g.x * inv, v.y = v.y * g.y * inv, v.z = v.z * g.z * inv, v.w = v.w * g.w * inv;
-                slot(i) = v;
+                float4 v = slot(0, i);
+                const float4 gg = __ldg(g4 + i);
+                v.x = v.x * gg.x * inv, v.y = v.y * gg.y * inv, v.z = v.z * gg.z * inv, v.w = v.w * gg.w * inv;
+                slot(0, i) = v;
             }
-        } else if (a.pro == 2) {
+        } else if (M == 1 && a.pro == 2) {
             // SwiGLU (silu = x / (1 + e^-x), compiler/src/interp.rs:13418) of a [gate | up] vector
             for (int i = threadIdx.x; i < n4; i += THREADS) {
-                const float4 g = __ldcg(x4 + i), u = __ldcg(x4 + n4 + i);
+                const float4 gt = __ldcg(x4 + i), up = __ldcg(x4 + n4 + i);
                 float4 v;
-                v.x = g.x / (1.0f + __expf(-g.x)) * u.x;
-                v.y = g.y / (1.0f + __expf(-g.y)) * u.y;
-                v.z = g.z / (1.0f + __expf(-g.z)) * u.z;
-                v.w = g.w / (1.0f + __expf(-g.w)) * u.w;
-                slot(i) = v;
+                v.x = gt.x / (1.0f + __expf(-gt.x)) * up.x;
+                v.y = gt.y / (1.0f + __expf(-gt.y)) * up.y;
+                v.z = gt.z / (1.0f + __expf(-gt.z)) * up.z;
+                v.w = gt.w / (1.0f + __expf(-gt.w)) * up.w;
+                slot(0, i) = v;
             }
         } else {
-            for (int i = threadIdx.x; i < n4; i += THREADS) slot(i) = __ldcg(x4 + i);
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+                for (int i = threadIdx.x; i < n4; i += THREADS) slot(m, i) = __ldcg(x4 + (size_t)m * n4 + i);
         }
         __syncthreads();
     }
 
-    bool first = true;  // the warp's first row group: chunk 0 is in registers, chunks 1..PF in shared memory
-    for (; row0 < rend; row0 += rstride) {
+    bool first = true;  // the warp's first row group: chunk 0 is already in registers
+    for (; g < g1; g += WARPS) {
+        const int row0 = g * R;
 #pragma unroll
-        for (int j = 0; j < R; ++j) acc[j] = 0.0f;
-        int it = 0;
-        for (int c = lane; c < nvec; c += 32 * U, ++it) {
-            if (first && it == 0) {
-                // already loaded before the dependency wait
-            } else if (PF > 0 && first && it <= PF) {
-                if (it == 1) asm volatile("cp.async.wait_group 0;" ::: "memory");
+        for (int j = 0; j < R; ++j)
 #pragma unroll
-                for (int j = 0; j < R; ++j)
+            for (int m = 0; m < M; ++m)
 #pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        const int cc = c + 32 * u;
-                        w[j][u] = (row0 + j < rend && cc < nvec) ? pf[(((it - 1) * R + j) * U + u) * 32 + lane]
-                                                                 : make_uint4(0, 0, 0, 0);
-                    }
-            } else {
-                load_w(row0, c);
-            }
+                for (int t = 0; t < NACC; ++t) acc[j][m][t] = 0.0f;
+        for (int c = lane; c < nvec; c += 32 * U) {
+            if (!(first && c == lane)) load_w(row0, c);
             consume(c);
         }
         first = false;
         float mine = 0.0f;  // sharded path: lane j keeps the sum of row j
 #pragma unroll
         for (int j = 0; j < R; ++j) {
-            float s = acc[j];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);  // every lane ends with the sum
-            const int row = row0 + j;
-            if (peer) {
-                if (lane == j) mine = s;
-            } else if (lane == 0 && row < rend) {
-                a.y[row] = s;
+            for (int m = 0; m < M; ++m) {
+                float s = acc[j][m][0];
+                if constexpr (NACC == 2) s += acc[j][m][1];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);  // every lane ends with the sum
+                const int row = row0 + j;
+                if (M == 1 && peer) {
+                    if (lane == j) mine = s;
+                } else if (lane == 0 && row < N) {
+                    a.y[(size_t)m * N + row] = s;
+                }
             }
         }
         // The R rows of a warp are adjacent, so lanes 0..R-1 store them together: one R*8-byte write per
         // replica instead of R separate ones (fewer, larger NVLink packets).
-        if (peer && lane < R && row0 + lane < rend) peer_store(peer, epoch, a.yoff + row0 + lane, mine);
+        if (M == 1 && peer && lane < R && row0 + lane < N) peer_store(peer, epoch, a.yoff + row0 + lane, mine);
     }
-    if (peer) peer_finish<THREADS>(peer, epoch, &s_last);
 }
 
 // Any-shape NK fallback: one warp per row, scalar loads.
 template <typename WT>
-__global__ void __launch_bounds__(256) gemv_nk_generic_kernel(const GemvArgs a, int M) {
+__global__ void __launch_bounds__(256) dmc_wrows_any_kernel(const GemvArgs a, int M) {
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
     griddep_wait();

@@ -1,6 +1,7 @@
 // gemv_launch.cu -- kernel-configuration tables and launch planning for the GEMV kernels.
 #include <algorithm>
 #include <cstdio>
+#include <set>
 
 #include "gemv.cuh"
 #include "gemv_tma.cuh"
@@ -23,17 +24,17 @@ struct KnVariant {
 #define KN_ROW(TK, U, V, CPS)                                                                    \
     {                                                                                            \
         "kn_tk" #TK "_u" #U "_v" #V, TK, U, V, CPS,                                              \
-            {gemv_kn_kernel<TK, U, V, 1, uint16_t>, nullptr, nullptr, nullptr},                  \
-            {gemv_kn_kernel<TK, U, V, 1, float>, nullptr, nullptr, nullptr},                     \
+            {dmc_wcols_kernel<TK, U, V, 1, uint16_t>, nullptr, nullptr, nullptr},                \
+            {dmc_wcols_kernel<TK, U, V, 1, float>, nullptr, nullptr, nullptr},                   \
     }
 
 // Index 0 is the multi-row-capable configuration (M up to 8).
 static const KnVariant kKn[] = {
     {"kn_tk8_u4_v1", 8, 4, 1, 4,
-     {gemv_kn_kernel<8, 4, 1, 1, uint16_t>, gemv_kn_kernel<8, 4, 1, 2, uint16_t>,
-      gemv_kn_kernel<8, 4, 1, 4, uint16_t>, gemv_kn_kernel<8, 4, 1, 8, uint16_t>},
-     {gemv_kn_kernel<8, 4, 1, 1, float>, gemv_kn_kernel<8, 4, 1, 2, float>,
-      gemv_kn_kernel<8, 4, 1, 4, float>, gemv_kn_kernel<8, 4, 1, 8, float>}},
+     {dmc_wcols_kernel<8, 4, 1, 1, uint16_t>, dmc_wcols_kernel<8, 4, 1, 2, uint16_t>,
+      dmc_wcols_kernel<8, 4, 1, 4, uint16_t>, dmc_wcols_kernel<8, 4, 1, 8, uint16_t>},
+     {dmc_wcols_kernel<8, 4, 1, 1, float>, dmc_wcols_kernel<8, 4, 1, 2, float>,
+      dmc_wcols_kernel<8, 4, 1, 4, float>, dmc_wcols_kernel<8, 4, 1, 8, float>}},
     KN_ROW(8, 8, 1, 4),
     KN_ROW(8, 4, 2, 2),
     KN_ROW(8, 8, 2, 2),
@@ -52,37 +53,61 @@ struct NkVariant {
     const char *name;
     int WARPS, R, U;
     KernelFn bf16, f32;
-    bool xg;  // x read from global memory (no shared-memory staging)
-    int pf;   // chunks of the first row group prefetched through shared memory before the dependency wait
 };
-#define NK_ROW(WARPS, R, U)                                                       \
-    {                                                                             \
-        "nk_w" #WARPS "_r" #R "_u" #U, WARPS, R, U,                               \
-            gemv_nk_kernel<WARPS, R, U, uint16_t>, gemv_nk_kernel<WARPS, R, U, float>, false, 0 \
-    }
-#define NK_ROWG(WARPS, R, U)                                                                  \
-    {                                                                                         \
-        "nk_w" #WARPS "_r" #R "_u" #U "_xg", WARPS, R, U,                                     \
-            gemv_nk_kernel<WARPS, R, U, uint16_t, true>, gemv_nk_kernel<WARPS, R, U, float, true>, true, 0 \
-    }
-#define NK_ROWPF(WARPS, R, U, PF)                                                             \
-    {                                                                                         \
-        "nk_w" #WARPS "_r" #R "_u" #U "_pf" #PF, WARPS, R, U,                                 \
-            gemv_nk_kernel<WARPS, R, U, uint16_t, false, PF>, gemv_nk_kernel<WARPS, R, U, float, false, PF>, false, PF \
+#define NK_ROW(WARPS, R, U)                                                                       \
+    {                                                                                             \
+        "nk_w" #WARPS "_r" #R "_u" #U, WARPS, R, U, dmc_wrows_kernel<WARPS, R, U, 1, uint16_t>,    \
+            dmc_wrows_kernel<WARPS, R, U, 1, float>                                               \
     }
 static const NkVariant kNk[] = {
-    NK_ROW(8, 2, 4),  NK_ROW(8, 1, 4),  NK_ROW(8, 1, 8),  NK_ROW(8, 2, 8),
-    NK_ROW(8, 4, 4),  NK_ROW(16, 1, 4), NK_ROW(16, 2, 4), NK_ROW(16, 1, 8),
-    NK_ROW(4, 2, 8),  NK_ROW(4, 4, 4),  NK_ROW(8, 4, 2),  NK_ROW(16, 2, 2),
-    NK_ROWG(8, 2, 8), NK_ROWG(8, 1, 16), NK_ROWG(16, 1, 8), NK_ROWG(8, 2, 4), NK_ROWG(4, 2, 8), NK_ROWG(8, 4, 4),
-    NK_ROWG(4, 1, 16), NK_ROWG(16, 2, 4),
-    NK_ROWPF(8, 2, 8, 1), NK_ROWPF(8, 2, 4, 3), NK_ROWPF(8, 1, 8, 1), NK_ROWPF(16, 1, 8, 1),
+    NK_ROW(8, 2, 8),  NK_ROW(8, 4, 4),  NK_ROW(8, 2, 4),  NK_ROW(8, 1, 8),
+    NK_ROW(8, 1, 4),  NK_ROW(16, 2, 4), NK_ROW(16, 1, 8), NK_ROW(4, 2, 8),
+    NK_ROW(4, 4, 4),  NK_ROW(8, 4, 2),
 };
 constexpr int kNkCount = sizeof(kNk) / sizeof(kNk[0]);
+constexpr size_t kNkMaxSmem = 200 * 1024;  // staged rows of x per CTA
+constexpr int kTcMinRows = 9;                // measured on B200 at 4096x4096: see the small-batch table of the benchmark
+
+// Small batches (2, 4 or 8 activation rows sharing every weight load), one configuration each.
+struct NkRows {
+    int M, WARPS, R, U;
+    KernelFn bf16, f32;
+};
+static const NkRows kNkRows[] = {
+    {2, 8, 2, 8, dmc_wrows_kernel<8, 2, 8, 2, uint16_t>, dmc_wrows_kernel<8, 2, 8, 2, float>},
+    {4, 8, 4, 4, dmc_wrows_kernel<8, 4, 4, 4, uint16_t>, dmc_wrows_kernel<8, 4, 4, 4, float>},
+    {8, 8, 4, 4, dmc_wrows_kernel<8, 4, 4, 8, uint16_t>, dmc_wrows_kernel<8, 4, 4, 8, float>},
+};
+
+// ---- which launches may overlap -----------------------------------------------------------
+// Address ranges read and written by the launches since the last point at which the stream was
+// known to be drained.  A GEMV that touches none of them in a conflicting way skips the
+// programmatic-dependency wait (GemvArgs::nowait) and overlaps whatever is still running; the first
+// launch that does conflict after such a kernel is made without the programmatic attribute, i.e.
+// it waits for everything before it.
+bool overlaps(const std::vector<AddrRange> &list, const void *p, size_t bytes) {
+    if (!p || !bytes) return false;
+    const uintptr_t lo = (uintptr_t)p, hi = lo + bytes;
+    for (const AddrRange &r : list)
+        if (lo < r.hi && r.lo < hi) return true;
+    return false;
+}
+void note(std::vector<AddrRange> &list, const void *p, size_t bytes) {
+    if (p && bytes) list.push_back(AddrRange{(uintptr_t)p, (uintptr_t)p + bytes});
+}
 
 }  // namespace
 
-int launch_ex(const void *fn, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, void **params) {
+void stream_drained() {
+    Context &c = ctx();
+    c.inflight_reads.clear();
+    c.inflight_writes.clear();
+    c.nowait_inflight = false;
+    c.untracked_inflight = false;
+}
+
+int launch_ex(const void *fn, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, void **params, int mode) {
+    Context &c = ctx();
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -90,7 +115,12 @@ int launch_ex(const void *fn, dim3 grid, dim3 block, size_t smem, cudaStream_t s
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     int nattr = 0;
-    if (tuning().pdl) {
+    // A kernel that must see everything before it, launched after kernels that skipped their wait,
+    // cannot rely on the chain of waits: it is launched fully serialised instead (so is one that
+    // arrives when the lists have grown long, which lets them be emptied).
+    const bool serialise = mode != kLaunchOverlap &&
+                           (c.nowait_inflight || c.inflight_reads.size() + c.inflight_writes.size() > kMaxTrackedRanges);
+    if (tuning().pdl && !serialise) {
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         nattr = 1;
@@ -98,7 +128,10 @@ int launch_ex(const void *fn, dim3 grid, dim3 block, size_t smem, cudaStream_t s
     cfg.attrs = attr;
     cfg.numAttrs = nattr;
     DMC_CUDA_TRY(cudaLaunchKernelExC(&cfg, fn, params));
-    ctx().launches++;
+    if (serialise) stream_drained();  // whatever ran before this kernel is complete when it starts
+    if (mode == kLaunchOverlap) c.nowait_inflight = true;
+    if (mode == kLaunchUntracked) c.untracked_inflight = true;
+    c.launches++;
     return DMC_CUDA_OK;
 }
 
@@ -107,20 +140,22 @@ int ensure_scratch(size_t partial_bytes, size_t ncounters) {
     if (partial_bytes > c.partial_cap) {
         // in-flight kernels may still use the old buffer
         DMC_CUDA_TRY(cudaStreamSynchronize(c.stream));
+        stream_drained();
         if (c.partial) cudaFree(c.partial);
         c.partial = nullptr;
         c.partial_cap = 0;
         size_t cap = std::max(partial_bytes, (size_t)4 << 20);
-        DMC_CUDA_TRY(cudaMalloc(&c.partial, cap));
+        DMC_CUDA_TRY(dmc_malloc((void **)&c.partial, cap));
         c.partial_cap = cap;
     }
     if (ncounters > c.counters_cap) {
         DMC_CUDA_TRY(cudaStreamSynchronize(c.stream));
+        stream_drained();
         if (c.counters) cudaFree(c.counters);
         c.counters = nullptr;
         c.counters_cap = 0;
         size_t cap = std::max(ncounters, (size_t)4096);
-        DMC_CUDA_TRY(cudaMalloc(&c.counters, cap * sizeof(unsigned)));
+        DMC_CUDA_TRY(dmc_malloc((void **)&c.counters, cap * sizeof(unsigned)));
         DMC_CUDA_TRY(cudaMemset(c.counters, 0, cap * sizeof(unsigned)));
         c.counters_cap = cap;
     }
@@ -129,7 +164,7 @@ int ensure_scratch(size_t partial_bytes, size_t ncounters) {
 
 namespace {
 
-// Default configuration per shape (from the B200 sweeps; see profiles/).
+// Default configuration per shape (from sweeps on B200 over every configuration in the tables above).
 int default_kn_variant(int64_t k, int64_t n) {
     (void)k;
     (void)n;
@@ -138,8 +173,8 @@ int default_kn_variant(int64_t k, int64_t n) {
 int default_nk_variant(int64_t k, int64_t n) {
     // B200 sweeps: 8 warps x 2 rows x 8 loads in flight is within ~2 % of the best configuration on
     // every decode shape; long rows of a big matrix do a little better with 4 rows x 4 loads.
-    if (k >= 8192 && n >= 8192) return 4;  // nk_w8_r4_u4
-    return 3;                              // nk_w8_r2_u8
+    if (k >= 8192 && n >= 8192) return 1;  // nk_w8_r4_u4
+    return 0;                              // nk_w8_r2_u8
 }
 
 int launch_kn(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
@@ -161,8 +196,8 @@ int launch_kn(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
         a.colblocks = (int)((n + 31) / 32);
         int M = (int)m;
         void *params[] = {&a, &M};
-        const void *fn = wdtype == DMC_W_BF16 ? (const void *)gemv_kn_generic_kernel<8, uint16_t>
-                                              : (const void *)gemv_kn_generic_kernel<8, float>;
+        const void *fn = wdtype == DMC_W_BF16 ? (const void *)dmc_wcols_any_kernel<8, uint16_t>
+                                              : (const void *)dmc_wcols_any_kernel<8, float>;
         return launch_ex(fn, dim3((unsigned)(a.colblocks * batch)), dim3(256), 0, stream, params);
     }
     if (variant < 0 || variant >= kKnCount) variant = default_kn_variant(k, n);
@@ -209,9 +244,9 @@ int launch_kn(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
 
 using TmaFn = void (*)(const GemvTmaArgs);
 #define TMA_ROW(T, CW)                                                                              \
-    {gemv_nk_tma_kernel<1, CW, T>, gemv_nk_tma_kernel<2, CW, T>, gemv_nk_tma_kernel<3, CW, T>,     \
-     gemv_nk_tma_kernel<4, CW, T>, gemv_nk_tma_kernel<5, CW, T>, gemv_nk_tma_kernel<6, CW, T>,     \
-     gemv_nk_tma_kernel<7, CW, T>, gemv_nk_tma_kernel<8, CW, T>}
+    {dmc_wrows_ring_kernel<1, CW, T>, dmc_wrows_ring_kernel<2, CW, T>, dmc_wrows_ring_kernel<3, CW, T>,     \
+     dmc_wrows_ring_kernel<4, CW, T>, dmc_wrows_ring_kernel<5, CW, T>, dmc_wrows_ring_kernel<6, CW, T>,     \
+     dmc_wrows_ring_kernel<7, CW, T>, dmc_wrows_ring_kernel<8, CW, T>}
 static const TmaFn kTma[2][2][8] = {  // [wdtype][CW == 16][VPL - 1]
     {TMA_ROW(uint16_t, 8), TMA_ROW(uint16_t, 16)},
     {TMA_ROW(float, 8), TMA_ROW(float, 16)},
@@ -296,16 +331,27 @@ int launch_nk_tma(const TmaPlan &p, const void *dW, const float *dx, float *dy, 
     return DMC_CUDA_OK;
 }
 
+// Grid of the NK kernel: one row group per warp when the whole matrix then fits in one wave of
+// resident CTAs (no warp idles, no CTA loops); otherwise exactly SMs x resident CTAs, every CTA
+// owning the same share of the row groups (the kernel splits them evenly by block index).
+int64_t nk_grid(int64_t n, int warps, int r, int sm_count, int cps) {
+    const int64_t groups = (n + r - 1) / r;
+    const int64_t exact = (groups + warps - 1) / warps;
+    const int64_t slots = (int64_t)sm_count * cps;
+    return std::max<int64_t>(1, exact <= slots ? exact : slots);
+}
+
 int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
               int wdtype, int variant, cudaStream_t stream) {
     Context &c = ctx();
     const int epv = wdtype == DMC_W_BF16 ? 8 : 4;
-    const size_t smem = (size_t)((k + 255) / 256 * 256) * sizeof(float);
+    const size_t xrow = (size_t)((k + 255) / 256 * 256) * sizeof(float);  // one staged row of x
     const bool vec_ok = k % epv == 0 && ((uintptr_t)dW % 16) == 0 && ((uintptr_t)dx % 16) == 0 &&
-                        smem <= 200 * 1024;
+                        xrow <= kNkMaxSmem;
     if (c.pro) {
-        if (!vec_ok) return fail(DMC_CUDA_ERR_UNSUPPORTED, "gemv: fused prologue needs k %% %d == 0 and aligned buffers", epv);
-        if (variant < 0 || variant >= kNkCount || kNk[variant].xg) variant = default_nk_variant(k, n);
+        if (!vec_ok || m != 1)
+            return fail(DMC_CUDA_ERR_UNSUPPORTED, "gemv: fused prologue needs m == 1, k %% %d == 0 and aligned buffers", epv);
+        if (variant < 0 || variant >= kNkCount) variant = default_nk_variant(k, n);
     }
     if (c.peer) {  // fused exchange lives in the vectorised LDG kernel only
         if (!vec_ok || m != 1)
@@ -328,44 +374,66 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
         a.y = dy;
         int M = (int)m;
         void *params[] = {&a, &M};
-        const void *fn = wdtype == DMC_W_BF16 ? (const void *)gemv_nk_generic_kernel<uint16_t>
-                                              : (const void *)gemv_nk_generic_kernel<float>;
+        const void *fn = wdtype == DMC_W_BF16 ? (const void *)dmc_wrows_any_kernel<uint16_t>
+                                              : (const void *)dmc_wrows_any_kernel<float>;
         return launch_ex(fn, dim3((unsigned)((n + 7) / 8)), dim3(256), 0, stream, params);
     }
     if (variant < 0 || variant >= kNkCount) variant = default_nk_variant(k, n);
-    const NkVariant &v = kNk[variant];
-    KernelFn fn = wdtype == DMC_W_BF16 ? v.bf16 : v.f32;
-    static bool attr_set[2][kNkCount] = {};
-    if (!attr_set[wdtype][variant]) {
-        DMC_CUDA_TRY(cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          200 * 1024));
-        attr_set[wdtype][variant] = true;
-    }
-    const size_t smem_used = (v.xg ? 0 : smem) + (size_t)v.pf * v.WARPS * v.R * v.U * 512;
-    if (smem_used > 200 * 1024) return fail(DMC_CUDA_ERR_UNSUPPORTED, "gemv: variant %s needs too much shared memory for k=%lld", v.name, (long long)k);
-    int by_threads = 2048 / (v.WARPS * 32);
-    int by_smem = (int)std::max<size_t>(1, (220 * 1024) / (smem_used + 1024));
-    int cps = std::min(by_threads, by_smem);
-    if (tuning().nk_ctas_per_sm > 0) cps = std::min(cps, tuning().nk_ctas_per_sm);
-    const int64_t groups = (n + (int64_t)v.WARPS * v.R - 1) / ((int64_t)v.WARPS * v.R);
-    int64_t grid = std::max<int64_t>(1, std::min<int64_t>(groups, (int64_t)c.sm_count * cps));
     a.peer = static_cast<const PeerOut *>(c.peer);
     a.yoff = c.peer_yoff;
     a.peer_j = c.peer_j;
-    if (c.pro) {
-        if (v.xg || m != 1) return fail(DMC_CUDA_ERR_UNSUPPORTED, "gemv: fused prologue needs the staged kernel and m == 1");
-        a.pro = c.pro;
-        a.pro_add = c.pro_add;
-        a.pro_g = c.pro_g;
-        a.pro_hout = c.pro_hout;
-        a.pro_eps = c.pro_eps;
-    }
-    for (int64_t mi = 0; mi < m; ++mi) {
-        a.x = dx + mi * k;
-        a.y = dy + mi * n;
+    a.pro = c.pro;
+    a.pro_add = c.pro_add;
+    a.pro_g = c.pro_g;
+    a.pro_hout = c.pro_hout;
+    a.pro_eps = c.pro_eps;
+    // rows of x are taken 8, 4, 2 or 1 at a time; every instance streams W once for its rows
+    for (int64_t m0 = 0; m0 < m;) {
+        const int64_t left = m - m0;
+        int M = left >= 8 ? 8 : left >= 4 ? 4 : left >= 2 ? 2 : 1;
+        while (M > 1 && (size_t)M * xrow > kNkMaxSmem) M >>= 1;  // the staged rows must fit in shared memory
+        KernelFn fn;
+        int warps, r;
+        if (M == 1) {
+            const NkVariant &v = kNk[variant];
+            fn = wdtype == DMC_W_BF16 ? v.bf16 : v.f32;
+            warps = v.WARPS, r = v.R;
+        } else {
+            const NkRows &v = kNkRows[M == 2 ? 0 : M == 4 ? 1 : 2];
+            fn = wdtype == DMC_W_BF16 ? v.bf16 : v.f32;
+            warps = v.WARPS, r = v.R;
+        }
+        const size_t smem = (size_t)M * xrow;
+        static std::set<const void *> smem_raised;  // once per kernel instance
+        if (!smem_raised.count((const void *)fn)) {
+            DMC_CUDA_TRY(cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNkMaxSmem));
+            smem_raised.insert((const void *)fn);
+        }
+        const int by_threads = 2048 / (warps * 32);
+        const int by_smem = (int)std::max<size_t>(1, (220 * 1024) / (smem + 1024));
+        int cps = std::min(2, std::min(by_threads, by_smem));  // the kernels use ~100-128 registers: two CTAs of 8 warps
+        if (tuning().nk_ctas_per_sm > 0) cps = std::min(std::min(by_threads, by_smem), tuning().nk_ctas_per_sm);
+        const int64_t grid = nk_grid(n, warps, r, c.sm_count, cps);
+        a.x = dx + m0 * k;
+        a.y = dy + m0 * n;
+        // May this launch overlap what is still running?  Only if nothing it reads is being written
+        // and nothing it writes is being read or written.
+        const size_t xbytes = (size_t)M * k * 4 * (a.pro == 2 ? 2 : 1), ybytes = (size_t)M * n * 4, hbytes = (size_t)k * 4;
+        const bool conflict = a.peer || !tuning().overlap_independent || c.untracked_inflight ||
+                              c.inflight_reads.size() + c.inflight_writes.size() > kMaxTrackedRanges ||
+                              overlaps(c.inflight_writes, a.x, xbytes) || overlaps(c.inflight_writes, a.pro_add, hbytes) ||
+                              overlaps(c.inflight_writes, a.y, ybytes) || overlaps(c.inflight_reads, a.y, ybytes) ||
+                              overlaps(c.inflight_writes, a.pro_hout, hbytes) || overlaps(c.inflight_reads, a.pro_hout, hbytes);
+        a.nowait = conflict ? 0 : 1;
         void *params[] = {&a};
-        int rc = launch_ex((const void *)fn, dim3((unsigned)grid), dim3(v.WARPS * 32), smem_used, stream, params);
+        int rc = launch_ex((const void *)fn, dim3((unsigned)grid), dim3(warps * 32), smem, stream, params,
+                           conflict ? kLaunchTracked : kLaunchOverlap);
         if (rc) return rc;
+        note(c.inflight_reads, a.x, xbytes);
+        note(c.inflight_reads, a.pro_add, hbytes);
+        note(c.inflight_writes, a.y, ybytes);
+        note(c.inflight_writes, a.pro_hout, hbytes);
+        m0 += M;
     }
     return DMC_CUDA_OK;
 }
@@ -374,7 +442,7 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
 
 bool nk_fast_eligible(int64_t k, int64_t n, int wdtype) {
     const int epv = wdtype == DMC_W_BF16 ? 8 : 4;
-    return n >= 1 && k >= 512 && k % epv == 0 && (size_t)((k + 255) / 256 * 256) * sizeof(float) <= 200 * 1024;
+    return n >= 1 && k >= 512 && k % epv == 0 && (size_t)((k + 255) / 256 * 256) * sizeof(float) <= kNkMaxSmem;
 }
 
 int launch_transpose(const void *src, void *dst, int64_t rows, int64_t cols, int elem_bytes, cudaStream_t stream) {
@@ -382,9 +450,9 @@ int launch_transpose(const void *src, void *dst, int64_t rows, int64_t cols, int
     dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
     if (grid.y > 65535) return fail(DMC_CUDA_ERR_UNSUPPORTED, "transpose: more than 4M rows");
     if (elem_bytes == 2)
-        transpose_kernel<uint16_t><<<grid, 256, 0, stream>>>((const uint16_t *)src, (uint16_t *)dst, (int)rows, (int)cols);
+        dmc_transpose_kernel<uint16_t><<<grid, 256, 0, stream>>>((const uint16_t *)src, (uint16_t *)dst, (int)rows, (int)cols);
     else
-        transpose_kernel<uint32_t><<<grid, 256, 0, stream>>>((const uint32_t *)src, (uint32_t *)dst, (int)rows, (int)cols);
+        dmc_transpose_kernel<uint32_t><<<grid, 256, 0, stream>>>((const uint32_t *)src, (uint32_t *)dst, (int)rows, (int)cols);
     DMC_CUDA_TRY(cudaGetLastError());
     ctx().launches++;
     return DMC_CUDA_OK;
@@ -406,10 +474,10 @@ int launch_gemv(const void *dW, const float *dx, float *dy, int64_t m, int64_t k
     if (layout == DMC_LAYOUT_KN) return launch_kn(dW, dx, dy, m, k, n, batch, ls, rs, wdtype, variant, stream);
     if (layout == DMC_LAYOUT_NK) {
         if (batch != 1) return fail(DMC_CUDA_ERR_UNSUPPORTED, "gemv: batched NK layout is not offered");
-        // several activation rows: a real contraction, which goes to the tensor cores.  Measured
-        // crossover on B200 at 4096x4096: with f32 activations (split in two bf16 terms) the tcgen05
-        // GEMM overtakes one GEMV per row from 3 rows up.
-        const int min_m = tuning().tc_min_m > 0 ? tuning().tc_min_m : 3;
+        // A few activation rows stay on the CUDA cores, with the exact f32 rows of x (the multi-row
+        // kernel streams W once for up to 8 rows).  From `tc_min_m` rows on the site is a real
+        // contraction and goes to the tensor cores, where x enters as two bf16 terms (16 mantissa bits).
+        const int min_m = tuning().tc_min_m > 0 ? tuning().tc_min_m : kTcMinRows;
         if (m >= min_m && wdtype == DMC_W_BF16 && variant < 0 && !ctx().peer && !ctx().pro && gemm_tc_eligible(m, k, n, dW, dx))
             return launch_gemm_tc_f32x(dW, dx, dy, m, k, n, stream);
         return launch_nk(dW, dx, dy, m, k, n, wdtype, variant, stream);

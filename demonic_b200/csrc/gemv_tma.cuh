@@ -97,7 +97,7 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
 // Dynamic shared memory: S*stage_bytes (ring) + S*SR*CW floats (warp partials).
 // Warps: CW consumers, one reducer (warp CW), one producer (warp CW+1).
 template <int VPL, int CW, typename WT>
-__global__ void __launch_bounds__((CW + 2) * 32, 1) gemv_nk_tma_kernel(const GemvTmaArgs a) {
+__global__ void __launch_bounds__((CW + 2) * 32, 1) dmc_wrows_ring_kernel(const GemvTmaArgs a) {
     constexpr int EPV = VecOf<WT>::EPV;
     constexpr int RU = 4;  // rows reduced together
     extern __shared__ __align__(128) unsigned char smem[];
@@ -250,7 +250,7 @@ __global__ void __launch_bounds__((CW + 2) * 32, 1) gemv_nk_tma_kernel(const Gem
 // Runs once per resident weight (the device-side counterpart of the reference's
 // `dmc_bf16_transpose_2d`, compiler/src/jit.rs:29801-29834; bit patterns preserved).
 template <typename T>
-__global__ void __launch_bounds__(256) transpose_kernel(const T *__restrict__ src, T *__restrict__ dst, int rows,
+__global__ void __launch_bounds__(256) dmc_transpose_kernel(const T *__restrict__ src, T *__restrict__ dst, int rows,
                                                          int cols) {
     __shared__ T tile[64][64 + 2];
     const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;

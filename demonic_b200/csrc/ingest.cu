@@ -346,9 +346,9 @@ extern "C" int dmc_cuda_load_npz(const char *path, const char *key, int64_t rows
         if (dev && !keep_dev) cudaFree(dev);
         close(fd);
     };
-    cudaError_t ce = cudaMalloc((void **)&dev, std::max<uint64_t>(total, 16));
+    cudaError_t ce = dmc_malloc((void **)&dev, std::max<uint64_t>(total, 16));
     // the ring outlives the call: pinning 64 MiB costs as much as reading a few hundred MiB
-    if (ce == cudaSuccess && !c.ingest_ring) ce = cudaMallocHost((void **)&c.ingest_ring, kRingBytes * kRingSlots);
+    if (ce == cudaSuccess && !c.ingest_ring) ce = dmc_malloc_host((void **)&c.ingest_ring, kRingBytes * kRingSlots);
     ring = c.ingest_ring;
     for (int i = 0; i < kRingSlots && ce == cudaSuccess; ++i) ce = cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming);
     if (ce != cudaSuccess) {

@@ -110,7 +110,7 @@ extern "C" int dmc_cuda_gemv_bf16_noalloc(const void *dW, const float *dx, float
     // The array keeps whatever the previous call left: the arrival counters must start at zero.
     // (The partial sums need no clearing; every slot that is read is written first.)
     DMC_CUDA_TRY(cudaMemsetAsync(scratch->counters, 0, sizeof(scratch->counters), s));
-    gemv_kn_kernel<TK, U, V, 1, uint16_t><<<dim3((unsigned)a.colblocks, (unsigned)ksplit), TK * 32, 0, s>>>(a);
+    dmc_wcols_kernel<TK, U, V, 1, uint16_t><<<dim3((unsigned)a.colblocks, (unsigned)ksplit), TK * 32, 0, s>>>(a);
     DMC_CUDA_TRY(cudaGetLastError());
     return DMC_CUDA_OK;
 }

@@ -30,6 +30,11 @@ struct RegisteredRange {
     size_t bytes;
     void *dev;
     int wdtype;
+    int64_t k = 0, n = 0;  // shape when the range is one [k, n] matrix stored k-contiguous on the device, else 0
+};
+
+struct AddrRange {
+    uintptr_t lo, hi;
 };
 
 struct PendingReadback {
@@ -43,6 +48,8 @@ struct Context {
     bool ready = false;
     cudaStream_t stream = nullptr;
     int sm_count = 148;
+    int clock_khz = 1900000;  // SM clock, converts the wait limit to clock64 cycles
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;  // per-call kernel timing (DMC_CUDA_TIME)
 
     // activation / output staging: pinned host mirrors of device buffers, bump-allocated
     // while deferred calls are outstanding (reference: compiler/src/gpu.rs:201-219)
@@ -77,6 +84,12 @@ struct Context {
     long long peer_yoff = 0;
     int peer_j = 0;
 
+    // Ranges the launches since the stream was last known to be drained read and write; decides which
+    // GEMVs may skip their dependency wait (gemv_launch.cu).
+    std::vector<AddrRange> inflight_reads, inflight_writes;
+    bool nowait_inflight = false;     // a kernel that skipped its wait has been launched since
+    bool untracked_inflight = false;  // so has a kernel whose ranges were not recorded
+
     // set by the decode step around a launch: elementwise prologue of the NK kernel's x staging
     int pro = 0;
     const float *pro_add = nullptr, *pro_g = nullptr;
@@ -105,11 +118,11 @@ struct Tuning {
     int tc_min_m = 0;       // activation rows from which `@` goes to the tensor cores (0 = library default)
     int zero_copy_y = 1;    // host-pointer entry points: kernels store y directly into pinned host memory
     int decode_fused = 1;   // decode step: fuse the companions into the GEMVs / attention (0 = one kernel per op)
-    int decode_debug = 0;   // measurement only: 1 = skip attention, 2 = skip argmax, 4 = no fused norm on the qkv GEMV
-    int shard_debug = 0;
-    int shard_exchange = 3; // fused exchange protocol, read at shard_init: 3 = tagged elements + gather kernel,
-                            // 2 = counted arrivals, 1 = flags by the last CTA
     int shard_fused = -1;   // sharded GEMV: 1 = peer stores fused into the kernel, 0 = NCCL all-gather, -1 = by world size
+    int overlap_independent = 1;  // GEMVs that touch nothing a running kernel touches skip their dependency wait
+    int wait_limit_us = 0;  // bound of the device-side waits on another rank, microseconds (0 = about one second)
+    int timing = 0;         // per-call phase timing printed to stderr (also DMC_CUDA_TIME=1)
+    int spin_sync = 1;      // host-pointer entry points poll the stream instead of blocking on it
 };
 
 Context &ctx();
@@ -129,6 +142,9 @@ int status();
     } while (0)
 
 int ensure_init();  // lazy dmc_cuda_init on the current device; returns status
+// Turn a code left in the pinned error word by a kernel whose bounded wait ran out into the sticky
+// DMC_CUDA_ERR_TIMEOUT; returns the status.
+int check_device_error();
 
 // Launch one GEMV (all pointers on the device).  batch slices at strides ls/rs elements.
 int launch_gemv(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
@@ -137,7 +153,22 @@ int launch_gemv(const void *dW, const float *dx, float *dy, int64_t m, int64_t k
 
 
 // One kernel launch with the library's launch attributes (programmatic dependent launch).
-int launch_ex(const void *fn, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, void **params);
+//   kLaunchUntracked  the kernel waits for its predecessors; what it reads and writes is not recorded
+//   kLaunchTracked    it waits; the caller has recorded its ranges in the context
+//   kLaunchOverlap    it skips its dependency wait (the caller checked that it conflicts with nothing in flight)
+enum { kLaunchUntracked = 0, kLaunchTracked = 1, kLaunchOverlap = 2 };
+constexpr size_t kMaxTrackedRanges = 1024;
+int launch_ex(const void *fn, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, void **params,
+              int mode = kLaunchUntracked);
+// The context's stream has been synchronised (or is about to run a fully serialising operation):
+// forget the recorded ranges.
+void stream_drained();
+// cudaMalloc / cudaMallocHost through one door, so that a test can make them fail on the host
+// (environment variable DMC_CUDA_INJECT, see dmc_cuda.cu).
+cudaError_t dmc_malloc(void **p, size_t bytes);
+cudaError_t dmc_malloc_host(void **p, size_t bytes);
+// True when DMC_CUDA_INJECT names `what` (comma-separated list).
+bool inject_failure(const char *what);
 // Grow the context's split-K scratch (partials in bytes, arrival counters in elements).
 int ensure_scratch(size_t partial_bytes, size_t ncounters);
 

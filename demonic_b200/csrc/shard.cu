@@ -8,10 +8,11 @@
 // this is the one exchange the path needs.  K is never split across ranks: that
 // would need a reduction of partial sums (more bytes, a second rounding order).
 //
-// Exchange mode 0: ncclAllGather (ragged splits: one ncclBroadcast per rank in a
-// group) on the context's stream.  NCCL is opened with dlopen so the library loads
-// on hosts without it; an already-loaded copy (e.g. the one PyTorch bundles) is
-// reused rather than loading a second one beside it.
+// Between GPUs with peer access the exchange is fused into the GEMV kernel (peer.cuh).
+// Otherwise, or on request, ncclAllGather (ragged splits: one ncclBroadcast per rank in a
+// group) follows the kernel on the context's stream.  NCCL is opened with dlopen so the
+// library loads on hosts without it; an already-loaded copy (e.g. the one PyTorch
+// bundles) is reused rather than loading a second one beside it.
 #include <dlfcn.h>
 
 #include <algorithm>
@@ -44,20 +45,19 @@ struct Shard {
     int rank = 0, world = 1;
     ncclComm_t comm = nullptr;
     // one allocation, shared with the peers through CUDA IPC:
-    //   [2 * max_n floats: y, double-buffered by epoch] [kMaxPeers flag words] [epoch] [CTA counter]
+    //   [2 * max_n floats: plain y, double-buffered by epoch] [tail: the epoch word] [2 * max_n tagged pairs]
     char *region = nullptr;
     float *y = nullptr;
     int64_t max_n = 0;
     void *peer_base[kMaxPeers] = {};  // peers' regions as mapped here (own entry = region)
     PeerOut *d_peer = nullptr;        // device copy of the exchange descriptor
     unsigned *d_epoch = nullptr;
-    int peer_mode = 3;  // 3: tagged elements + gather kernel (default); 2: counted arrivals; 1: flag exchange by the last CTA
-    bool fused_ok = false;            // peer mappings are in place
+    bool fused_ok = false;            // peer mappings are in place on EVERY rank (agreed at init)
     bool last_fused = false;          // which buffer holds the latest result
 };
 constexpr size_t kTailBytes = 256;
 
-// [y: 2 * max_n floats][tail: flags, epoch, counters][tagged y: 2 * max_n pairs]
+// [y: 2 * max_n floats][tail: epoch word][tagged y: 2 * max_n pairs]
 size_t region_bytes(int64_t max_n) { return (size_t)2 * max_n * sizeof(float) + kTailBytes + (size_t)2 * max_n * 8; }
 
 NcclApi g_nccl;
@@ -95,31 +95,20 @@ int load_nccl() {
             return fail(DMC_CUDA_ERR_NCCL, "%s failed: %s", #expr, g_nccl.GetErrorString(r__));  \
     } while (0)
 
+// Whether a sharded GEMV uses the exchange fused into the kernel.  Every argument has the same value
+// on every rank (`fused_ok` is the AND over all ranks, agreed in shard_init), so every rank takes the
+// same path; n < world (some slices empty) keeps the fused path too, the empty ranks just store nothing.
+bool fused_path_chosen(int world, bool fused_ok, int shard_fused, int64_t k, int64_t n) {
+    const bool want = shard_fused < 0 ? world >= 2 : shard_fused != 0;
+    return want && fused_ok && k > 0 && n > 0;
+}
+
 void shard_range(int64_t n, int rank, int world, int64_t *r0, int64_t *r1) {
     *r0 = n * rank / world;
     *r1 = n * (rank + 1) / world;
 }
 
-// Local GEMV into y[r0, r1) then the exchange, all on `s`.
-// Closes an exchange for consumers that are not themselves a sharded GEMV: returns once every rank's
-// share of the current epoch has been counted here.  One thread.
-__global__ void peer_wait_kernel(const PeerOut *p) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (threadIdx.x != 0 || (p->debug & 2)) return;
-    const unsigned e = __ldcg(p->epoch);
-    const unsigned target = e * (unsigned)p->world * kPeerQuantum;
-    const unsigned *mine = p->flags[p->rank];
-    const long long t0 = clock64();
-    while ((int)(ld_acquire_sys(mine) - target) < 0) {
-        if (clock64() - t0 > (1LL << 31)) {
-            *(volatile int *)p->err = 5;
-            break;
-        }
-    }
-}
-
-// mode 3: the replicated y arrives as {value, epoch} pairs written by every rank's GEMV.  This kernel
+// The replicated y arrives as {value, epoch} pairs written by every rank's GEMV.  This kernel
 // does not wait for the local GEMV to complete (whose completion includes the acknowledgement of its
 // remote stores): it runs beside it, and re-reads each pair (bounded) until it carries the epoch of
 // this exchange, then writes the plain y of that epoch's parity.  j: position of the exchange in the
@@ -131,17 +120,17 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const PeerOut *p, int 
     const unsigned long long *src = p->ty[p->rank] + (size_t)(e & 1u) * p->stride;
     float *dst = p->yplain + (size_t)(e & 1u) * p->stride;
     const int pairs2 = n / 2;  // 16-byte pieces
-    const bool skip = (p->debug & 2) != 0;
+    const long long limit = p->wait_cycles;
     const int first = blockIdx.x * blockDim.x;
     // While the GEMVs are still streaming, one thread per CTA watches one piece at a relaxed pace, so
     // that the 32K threads of this grid do not load L2 for the whole duration of the GEMV.
-    if (threadIdx.x == 0 && first < pairs2 && !skip) {
+    if (threadIdx.x == 0 && first < pairs2) {
         const long long t0 = clock64();
         for (;;) {
             unsigned a0, a1, b0, b1;
             asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(b0), "=r"(b1) : "l"(src + 2 * (size_t)first) : "memory");
             if (a1 == e && b1 == e) break;
-            if (clock64() - t0 > (1LL << 31)) break;  // the loop below reports it
+            if (clock64() - t0 > limit) break;  // the loop below reports it
             __nanosleep(200);
         }
     }
@@ -151,8 +140,8 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const PeerOut *p, int 
         const long long t0 = clock64();
         for (;;) {
             asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(b0), "=r"(b1) : "l"(src + 2 * (size_t)i) : "memory");
-            if ((a1 == e && b1 == e) || skip) break;
-            if (clock64() - t0 > (1LL << 31)) {  // ~1 s: give up instead of hanging
+            if (a1 == e && b1 == e) break;
+            if (clock64() - t0 > limit) {  // give up instead of hanging: the host reads the error word
                 *(volatile int *)p->err = 6;
                 break;
             }
@@ -165,8 +154,8 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const PeerOut *p, int 
         const long long t0 = clock64();
         for (;;) {
             asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(src + (n - 1)) : "memory");
-            if ((unsigned)(v >> 32) == e || skip) break;
-            if (clock64() - t0 > (1LL << 31)) {
+            if ((unsigned)(v >> 32) == e) break;
+            if (clock64() - t0 > limit) {
                 *(volatile int *)p->err = 6;
                 break;
             }
@@ -176,7 +165,7 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const PeerOut *p, int 
     }
 }
 
-// mode 3: closes a batch of `count` exchanges.  Waits for everything before it, then advances the
+// Closes a batch of `count` exchanges.  Waits for everything before it, then advances the
 // epoch word -- before any kernel of the next batch can start, since those launch only after the
 // launch_dependents below.
 __global__ void peer_batch_end_kernel(const PeerOut *p, int count) {
@@ -199,21 +188,25 @@ int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, i
     int64_t r0, r1;
     shard_range(n, sh.rank, sh.world, &r0, &r1);
     // Measured on B200 (65536x8192): the fused exchange is ahead of ncclAllGather from 2 ranks up
-    // (89.5 vs 95.4 us at 2, 26.0 vs 42.5 us at 8).
-    const bool want_fused = tuning().shard_fused < 0 ? sh.world >= 2 : tuning().shard_fused != 0;
-    if (want_fused && sh.fused_ok && r1 > r0 && k > 0) {
-        // one kernel: GEMV whose epilogue stores into every replica and closes with the flag exchange
+    // (89.5 vs 95.4 us at 2, 26.0 vs 42.5 us at 8).  The choice uses only facts that are the same on
+    // every rank -- a rank that took the other path would leave its peers waiting for it.
+    if (fused_path_chosen(sh.world, sh.fused_ok, tuning().shard_fused, k, n)) {
+        // one kernel: GEMV whose epilogue stores into every replica; the gather kernel beside it
+        // validates the arrivals.  A rank whose slice is empty still runs the gather and the batch
+        // end, so its epoch stays in step with its peers.
         Context &c = ctx();
-        c.peer = sh.d_peer;
-        c.peer_yoff = r0;
-        c.peer_j = j;
-        const int mode = sh.peer_mode;
-        int rc = launch_gemv(dW_shard, dx, sh.y + r0, 1, k, r1 - r0, 1, 0, 0, DMC_LAYOUT_NK, wdtype, -1, s);
-        c.peer = nullptr;
-        c.peer_yoff = 0;
-        c.peer_j = 0;
+        int rc = DMC_CUDA_OK;
+        if (r1 > r0) {
+            c.peer = sh.d_peer;
+            c.peer_yoff = r0;
+            c.peer_j = j;
+            rc = launch_gemv(dW_shard, dx, sh.y + r0, 1, k, r1 - r0, 1, 0, 0, DMC_LAYOUT_NK, wdtype, -1, s);
+            c.peer = nullptr;
+            c.peer_yoff = 0;
+            c.peer_j = 0;
+        }
         sh.last_fused = true;
-        if (rc == DMC_CUDA_OK && mode == 3) {
+        if (rc == DMC_CUDA_OK) {
             const PeerOut *pp = sh.d_peer;
             int rows = (int)n, jj = j;
             void *params[] = {&pp, &rows, &jj};
@@ -225,17 +218,13 @@ int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, i
                 rc = launch_ex((const void *)peer_batch_end_kernel, dim3(1), dim3(32), 0, s, params2);
             }
         }
-        if (rc == DMC_CUDA_OK && mode == 2 && end_batch) {
-            const PeerOut *pp = sh.d_peer;
-            void *params[] = {&pp};
-            rc = launch_ex((const void *)peer_wait_kernel, dim3(1), dim3(32), 0, s, params);
-        }
         return rc;
     }
     sh.last_fused = false;
     int rc = launch_gemv(dW_shard, dx, sh.y + r0, 1, k, r1 - r0, 1, 0, 0, DMC_LAYOUT_NK, wdtype, -1, s);
     if (rc) return rc;
     if (sh.world == 1) return DMC_CUDA_OK;
+    ctx().untracked_inflight = true;  // the collective below writes y outside the launch planner's view
     if (n % sh.world == 0) {
         DMC_NCCL_TRY(g_nccl.AllGather(sh.y + r0, sh.y, (size_t)(n / sh.world), ncclFloat32, sh.comm, s));
     } else {  // ragged: every rank broadcasts its slice
@@ -277,18 +266,26 @@ extern "C" int dmc_cuda_shard_unique_id(uint8_t *out128) {
     return DMC_CUDA_OK;
 }
 
-extern "C" int dmc_cuda_shard_init(int rank, int world, const uint8_t *id128, int64_t max_n) {
-    std::lock_guard<std::mutex> lock(ctx_mutex());
-    if (dmc::status()) return dmc::status();
-    if (world < 1 || rank < 0 || rank >= world || max_n < 1)
-        return fail(DMC_CUDA_ERR_BAD_ARG, "shard_init: bad rank %d / world %d / max_n %lld", rank, world, (long long)max_n);
-    int rc = ensure_init();
-    if (rc) return rc;
+namespace dmc {
+namespace {
+
+void shard_release(Shard &sh) {
+    for (int r = 0; r < sh.world && r < kMaxPeers; ++r)
+        if (r != sh.rank && sh.peer_base[r]) cudaIpcCloseMemHandle(sh.peer_base[r]);
+    if (sh.comm) g_nccl.CommDestroy(sh.comm);
+    if (sh.d_peer) cudaFree(sh.d_peer);
+    if (sh.region) cudaFree(sh.region);
+    sh = Shard();
+}
+
+int shard_init_locked(int rank, int world, const uint8_t *id128, int64_t max_n) {
     Shard &sh = g_shard;
-    if (sh.ready) return fail(DMC_CUDA_ERR_BAD_ARG, "shard_init: already initialised");
-    if (world > 1) {
+    sh.rank = rank;
+    sh.world = world;
+    if (world > 1 || inject_failure("nccl_init")) {
+        if (inject_failure("nccl_init")) return fail(DMC_CUDA_ERR_NCCL, "ncclCommInitRank failed: injected");
         if (!id128) return fail(DMC_CUDA_ERR_BAD_ARG, "shard_init: world > 1 needs the 128-byte NCCL id");
-        rc = load_nccl();
+        int rc = load_nccl();
         if (rc) return rc;
         ncclUniqueId id;
         memcpy(id.internal, id128, 128);
@@ -296,69 +293,106 @@ extern "C" int dmc_cuda_shard_init(int rank, int world, const uint8_t *id128, in
     }
     max_n = (max_n + 3) & ~(int64_t)3;  // keeps both halves of every double buffer 16-byte aligned
     const size_t bytes = region_bytes(max_n);
-    DMC_CUDA_TRY(cudaMalloc((void **)&sh.region, bytes));
+    DMC_CUDA_TRY(dmc_malloc((void **)&sh.region, bytes));
     DMC_CUDA_TRY(cudaMemset(sh.region, 0, bytes));
     sh.y = reinterpret_cast<float *>(sh.region);
     sh.max_n = max_n;
-    sh.rank = rank;
-    sh.world = world;
     sh.peer_base[rank] = sh.region;
-    sh.fused_ok = world <= kMaxPeers;
-    if (world > 1 && sh.fused_ok) {
+    bool mine_ok = world <= kMaxPeers && !inject_failure("ipc_open");
+    cudaStream_t s = ctx().stream;
+    if (world > 1) {
         // exchange the IPC handle of the region through the communicator itself
         cudaIpcMemHandle_t mine, all[kMaxPeers];
-        DMC_CUDA_TRY(cudaIpcGetMemHandle(&mine, sh.region));
         char *d_h = nullptr;
-        DMC_CUDA_TRY(cudaMalloc((void **)&d_h, sizeof(mine) * world));
-        DMC_CUDA_TRY(cudaMemcpy(d_h + sizeof(mine) * rank, &mine, sizeof(mine), cudaMemcpyHostToDevice));
-        cudaStream_t s = ctx().stream;
-        DMC_NCCL_TRY(g_nccl.AllGather(d_h + sizeof(mine) * rank, d_h, sizeof(mine), ncclUint8, sh.comm, s));
-        DMC_CUDA_TRY(cudaStreamSynchronize(s));
-        DMC_CUDA_TRY(cudaMemcpy(all, d_h, sizeof(mine) * world, cudaMemcpyDeviceToHost));
-        cudaFree(d_h);
-        for (int r = 0; r < world; ++r) {
-            if (r == rank) continue;
-            cudaError_t e = cudaIpcOpenMemHandle(&sh.peer_base[r], all[r], cudaIpcMemLazyEnablePeerAccess);
-            if (e != cudaSuccess) {  // no peer access between these GPUs: keep the NCCL exchange
-                cudaGetLastError();
-                sh.fused_ok = false;
-                break;
+        if (mine_ok) {
+            DMC_CUDA_TRY(cudaIpcGetMemHandle(&mine, sh.region));
+            DMC_CUDA_TRY(dmc_malloc((void **)&d_h, sizeof(mine) * world));
+            DMC_CUDA_TRY(cudaMemcpy(d_h + sizeof(mine) * rank, &mine, sizeof(mine), cudaMemcpyHostToDevice));
+            DMC_NCCL_TRY(g_nccl.AllGather(d_h + sizeof(mine) * rank, d_h, sizeof(mine), ncclUint8, sh.comm, s));
+            DMC_CUDA_TRY(cudaStreamSynchronize(s));
+            DMC_CUDA_TRY(cudaMemcpy(all, d_h, sizeof(mine) * world, cudaMemcpyDeviceToHost));
+            cudaFree(d_h);
+            for (int r = 0; r < world; ++r) {
+                if (r == rank) continue;
+                cudaError_t e = cudaIpcOpenMemHandle(&sh.peer_base[r], all[r], cudaIpcMemLazyEnablePeerAccess);
+                if (e != cudaSuccess) {  // no peer access between these GPUs: keep the NCCL exchange
+                    cudaGetLastError();
+                    sh.peer_base[r] = nullptr;
+                    mine_ok = false;
+                    break;
+                }
             }
         }
+        // Every rank must take the same path in every later call: the fused exchange is used only
+        // if the mappings are in place on all of them (one byte per rank, gathered; AND).
+        unsigned char *d_ok = nullptr, ok_all[kMaxPeers + 56] = {};
+        const size_t slots = (size_t)std::max(world, 1);
+        DMC_CUDA_TRY(dmc_malloc((void **)&d_ok, slots));
+        const unsigned char ok_byte = mine_ok ? 1 : 0;
+        DMC_CUDA_TRY(cudaMemcpy(d_ok + rank, &ok_byte, 1, cudaMemcpyHostToDevice));
+        DMC_NCCL_TRY(g_nccl.AllGather(d_ok + rank, d_ok, 1, ncclUint8, sh.comm, s));
+        DMC_CUDA_TRY(cudaStreamSynchronize(s));
+        DMC_CUDA_TRY(cudaMemcpy(ok_all, d_ok, std::min(slots, sizeof(ok_all)), cudaMemcpyDeviceToHost));
+        cudaFree(d_ok);
+        sh.fused_ok = world <= kMaxPeers;
+        for (int r = 0; r < world && r < (int)sizeof(ok_all); ++r) sh.fused_ok = sh.fused_ok && ok_all[r] != 0;
+    } else {
+        sh.fused_ok = mine_ok;
     }
     if (sh.fused_ok) {
         PeerOut po = {};
-        for (int r = 0; r < world; ++r) {
-            char *base = static_cast<char *>(sh.peer_base[r]);
-            po.y[r] = reinterpret_cast<float *>(base);
-            po.flags[r] = reinterpret_cast<unsigned *>(base + (size_t)2 * max_n * sizeof(float));
-            po.ty[r] = reinterpret_cast<unsigned long long *>(base + (size_t)2 * max_n * sizeof(float) + kTailBytes);
-        }
+        for (int r = 0; r < world; ++r)
+            po.ty[r] = reinterpret_cast<unsigned long long *>(static_cast<char *>(sh.peer_base[r]) +
+                                                              (size_t)2 * max_n * sizeof(float) + kTailBytes);
         po.yplain = sh.y;
-        unsigned *tail = reinterpret_cast<unsigned *>(sh.region + (size_t)2 * max_n * sizeof(float));
-        po.epoch = tail + kMaxPeers;
-        po.counter = tail + kMaxPeers + 1;
+        po.epoch = reinterpret_cast<unsigned *>(sh.region + (size_t)2 * max_n * sizeof(float));
         po.err = ctx().err_word;
         po.stride = max_n;
+        // bound of the gather kernel's wait for its peers: "wait_limit_us", by default about a second
+        const long long us = tuning().wait_limit_us > 0 ? tuning().wait_limit_us : 1000000;
+        po.wait_cycles = us * (long long)(ctx().clock_khz / 1000);
         po.world = world;
         po.rank = rank;
-        po.debug = tuning().shard_debug;
-        // the two fused protocols keep different state in the flag words: the choice is made once, here
-        {
-            const int want = tuning().shard_exchange;
-            po.mode = sh.peer_mode = (want >= 1 && want <= 3) ? want : 3;
-        }
         sh.d_epoch = po.epoch;
-        DMC_CUDA_TRY(cudaMalloc((void **)&sh.d_peer, sizeof(PeerOut)));
+        DMC_CUDA_TRY(dmc_malloc((void **)&sh.d_peer, sizeof(PeerOut)));
         DMC_CUDA_TRY(cudaMemcpy(sh.d_peer, &po, sizeof(po), cudaMemcpyHostToDevice));
     }
-    if (world > 1) {  // nobody may store into a peer before that peer has zeroed its flags
-        DMC_NCCL_TRY(g_nccl.AllGather(sh.y + rank, sh.y, 1, ncclFloat32, sh.comm, ctx().stream));
-        DMC_CUDA_TRY(cudaStreamSynchronize(ctx().stream));
+    if (world > 1) {  // nobody may store into a peer before that peer has zeroed its region
+        DMC_NCCL_TRY(g_nccl.AllGather(sh.y + rank, sh.y, 1, ncclFloat32, sh.comm, s));
+        DMC_CUDA_TRY(cudaStreamSynchronize(s));
         DMC_CUDA_TRY(cudaMemset(sh.y, 0, (size_t)world * sizeof(float)));
     }
+    stream_drained();
     sh.ready = true;
     return DMC_CUDA_OK;
+}
+
+}  // namespace
+}  // namespace dmc
+
+extern "C" int dmc_cuda_shard_init(int rank, int world, const uint8_t *id128, int64_t max_n) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return dmc::status();
+    if (world < 1 || rank < 0 || rank >= world || max_n < 1)
+        return fail(DMC_CUDA_ERR_BAD_ARG, "shard_init: bad rank %d / world %d / max_n %lld", rank, world, (long long)max_n);
+    int rc = ensure_init();
+    if (rc) return rc;
+    if (g_shard.ready) return fail(DMC_CUDA_ERR_BAD_ARG, "shard_init: already initialised");
+    rc = shard_init_locked(rank, world, id128, max_n);
+    if (rc) shard_release(g_shard);  // nothing half-built stays behind a failed init
+    return rc;
+}
+
+// 1 when sharded GEMVs of this size would use the exchange fused into the kernel, 0 for the NCCL exchange.
+extern "C" int dmc_cuda_shard_uses_fused(int64_t k, int64_t n) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (!g_shard.ready) return 0;
+    return fused_path_chosen(g_shard.world, g_shard.fused_ok, tuning().shard_fused, k, n) ? 1 : 0;
+}
+
+// The same decision from explicit facts (pure; no device): lets a host check that every rank would agree.
+extern "C" int dmc_cuda_shard_path(int world, int peer_access_everywhere, int shard_fused, int64_t k, int64_t n) {
+    return fused_path_chosen(world, peer_access_everywhere != 0, shard_fused, k, n) ? 1 : 0;
 }
 
 extern "C" void dmc_cuda_shard_shutdown(void) {
@@ -366,12 +400,8 @@ extern "C" void dmc_cuda_shard_shutdown(void) {
     Shard &sh = g_shard;
     if (!sh.ready) return;
     if (ctx().ready) cudaStreamSynchronize(ctx().stream);
-    for (int r = 0; r < sh.world && r < kMaxPeers; ++r)
-        if (r != sh.rank && sh.peer_base[r]) cudaIpcCloseMemHandle(sh.peer_base[r]);
-    if (sh.comm) g_nccl.CommDestroy(sh.comm);
-    if (sh.d_peer) cudaFree(sh.d_peer);
-    if (sh.region) cudaFree(sh.region);
-    sh = Shard();
+    stream_drained();
+    shard_release(sh);
 }
 
 extern "C" float *dmc_cuda_shard_output(void) {
@@ -385,6 +415,38 @@ extern "C" float *dmc_cuda_shard_output(void) {
     cudaStreamSynchronize(ctx().stream);
     cudaMemcpy(&e, sh.d_epoch, sizeof(e), cudaMemcpyDeviceToHost);
     return sh.y + (size_t)(e & 1u) * sh.max_n;
+}
+
+// Self-test of the bounded waits: run the gather for an exchange that no GEMV writes.  Every thread of
+// it re-reads its pair until the configured limit ("wait_limit_us" at shard_init) runs out, records the
+// error word and returns; the host then reports DMC_CUDA_ERR_TIMEOUT like any other failed call.
+// Nothing faults or hangs, the context stays usable (clear the error and carry on).
+extern "C" int dmc_cuda_shard_probe_timeout(int64_t n) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return dmc::status();
+    Shard &sh = g_shard;
+    if (!sh.ready || !sh.fused_ok || n < 1 || n > sh.max_n)
+        return fail(DMC_CUDA_ERR_BAD_ARG, "shard_probe_timeout: needs dmc_cuda_shard_init with the fused exchange and 1 <= n <= max_n");
+    const PeerOut *pp = sh.d_peer;
+    int rows = (int)n, far = 1 << 20;  // an epoch a million exchanges ahead: nobody has written it
+    void *params[] = {&pp, &rows, &far};
+    const int ctas = (int)std::max<int64_t>(1, std::min<int64_t>(128, (n / 2 + 255) / 256));
+    int rc = launch_ex((const void *)peer_gather_kernel, dim3(ctas), dim3(256), 0, ctx().stream, params);
+    if (rc) return rc;
+    DMC_CUDA_TRY(cudaStreamSynchronize(ctx().stream));
+    stream_drained();
+    return check_device_error();
+}
+
+extern "C" float *dmc_cuda_shard_output_previous(void) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    Shard &sh = g_shard;
+    if (!sh.ready) return nullptr;
+    cudaStreamSynchronize(ctx().stream);
+    if (!sh.last_fused) return sh.y;
+    unsigned e = 0;
+    cudaMemcpy(&e, sh.d_epoch, sizeof(e), cudaMemcpyDeviceToHost);
+    return sh.y + (size_t)((e + 1u) & 1u) * sh.max_n;
 }
 
 extern "C" int dmc_cuda_shard_gemv(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype) {
@@ -408,8 +470,6 @@ extern "C" double dmc_cuda_bench_shard(const void *const *dW_shards, int copies,
     cudaGraphExec_t exec = nullptr;
     double us = -1.0;
     auto one_step = [&]() -> int {
-        // with the counted exchange every GEMV begins by waiting for the previous exchange to have landed,
-        // so only the last one of the step needs the separate closing wait
         for (int i = 0; i < copies; ++i) {
             int rc = shard_gemv_on(dW_shards[i], dx, k, n, wdtype, s, i, i == copies - 1);
             if (rc) return rc;
@@ -420,6 +480,7 @@ extern "C" double dmc_cuda_bench_shard(const void *const *dW_shards, int copies,
         int rc = one_step();  // eager: sizes scratch, lets NCCL set up its channels
         if (rc) return rc;
         DMC_CUDA_TRY(cudaStreamSynchronize(s));
+        stream_drained();
         DMC_CUDA_TRY(cudaEventCreate(&e0));
         DMC_CUDA_TRY(cudaEventCreate(&e1));
         int64_t per_step = 0;
@@ -428,6 +489,7 @@ extern "C" double dmc_cuda_bench_shard(const void *const *dW_shards, int copies,
             DMC_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
             rc = one_step();
             cudaError_t ce = cudaStreamEndCapture(s, &graph);
+            stream_drained();
             if (rc) return rc;
             DMC_CUDA_TRY(ce);
             per_step = c.launches - before;

@@ -53,6 +53,15 @@ def output(n: int) -> np.ndarray:
     return out
 
 
+def output_previous(n: int) -> np.ndarray:
+    """The replicated y of the sharded GEMV before the last one (the other buffer of the pair)."""
+    lib = _lib.load()
+    out = np.empty(n, np.float32)
+    lib.dmc_cuda_d2h(out.ctypes.data_as(C.c_void_p), lib.dmc_cuda_shard_output_previous(), out.nbytes)
+    _lib.check()
+    return out
+
+
 def bench(dW_shards: list[backend.DeviceBuffer], dx: backend.DeviceBuffer, k: int, n: int, steps: int,
           warmup: int, use_graph: bool = True, wdtype: int = backend.W_BF16) -> float:
     arr = (C.c_void_p * len(dW_shards))(*[b.ptr for b in dW_shards])

@@ -14,6 +14,10 @@
  * `out` untouched and records a sticky status readable with
  * dmc_cuda_status() / dmc_cuda_last_error(); the host turns a non-zero status
  * into its `runtime error: ...` + exit(1) convention.
+ *
+ * Testing error paths without touching the device: the environment variable
+ * DMC_CUDA_INJECT (comma-separated: malloc, malloc_host, stream, nccl_init,
+ * ipc_open) makes the named host-side calls report failure without being made.
  */
 #ifndef DMC_CUDA_H
 #define DMC_CUDA_H
@@ -80,13 +84,22 @@ void dmc_cuda_clear_error(void);
  * CPU `dmc_matmul_bf16`, compiler/src/jit.rs:29488).  Unlike the reference,
  * m > 1 also runs on the GPU.  Weights are uploaded on first sight and kept
  * resident, keyed by the reference's content fingerprint
- * (compiler/src/gpu.rs:342-358) or by a registered range (below). */
+ * (compiler/src/gpu.rs:342-358) or by a registered range (below).
+ *
+ * Arithmetic by row count (the reference multiplies f32 l by the widened weight in every case):
+ * m <= 8 runs on the CUDA cores with the exact f32 rows of l; from m = 9 on (the "tc_min_m" knob)
+ * a k-contiguous resident bf16 weight goes to the tensor cores, where each element of l enters as the
+ * sum of two bf16 terms, i.e. to 16 mantissa bits instead of 24.  Measured difference from the
+ * reference < 1e-4 of max|y|, inside the 1e-2 bound stated for bf16 weights; a host that needs the
+ * CUDA-core arithmetic for every m sets tc_min_m above its largest m. */
 void dmc_matmul_bf16_gpu(int64_t l, int64_t r, int64_t out, int64_t m, int64_t k, int64_t n);
 
 /* `batch` m==1 slices in one launch: slice z reads l + z*ls (f32 elements),
  * r + z*rs (bf16 elements) and writes out + z*n; ls / rs may be 0 (broadcast
  * operand).  Replaces `dmc_matmul_bf16_gpu_batched`,
- * compiler/src/gpu.rs:421-439. */
+ * compiler/src/gpu.rs:421-439.  With m != 1 the slices (l + z*ls, r + z*rs ->
+ * out + z*m*n) run one after the other, as the reference does (gpu.rs:428-437),
+ * but on the GPU. */
 void dmc_matmul_bf16_gpu_batched(int64_t l, int64_t r, int64_t out, int64_t m, int64_t k, int64_t n,
                                  int64_t batch, int64_t ls, int64_t rs);
 
@@ -119,8 +132,8 @@ void dmc_matmul_bf16_gpu_nt(int64_t l, int64_t w, int64_t out, int64_t m, int64_
  * no enclosing `@deterministic`, and the work clears the offload threshold.
  * Mirrors `blas_gemm_selected` (compiler/src/jit.rs:29346-29351) for the depth
  * rule and the `--gpu` gates for the sizes: single GEMV needs k*n >= 4e6
- * (compiler/src/jit.rs:20933-20934), a batched projection batch*m*k*n >= 1e6
- * and batch <= 65536 (compiler/src/jit.rs:19912-19915).  `rhs_bf16` = 0 asks
+ * (compiler/src/jit.rs:20933-20934), a batched projection m == 1, n % 4 == 0,
+ * batch*k*n >= 1e6 and batch <= 65536 (compiler/src/jit.rs:19912-19915).  `rhs_bf16` = 0 asks
  * about an f32 `@` site (threshold: BLAS_MIN_MACS = 2^17, compiler/src/jit.rs:29340). */
 int dmc_cuda_matmul_selected(int flag_on, uint32_t deterministic_depth, int64_t m, int64_t k,
                              int64_t n, int64_t batch, int rhs_bf16);
@@ -130,8 +143,13 @@ int dmc_cuda_matmul_selected(int flag_on, uint32_t deterministic_depth, int64_t 
 /* Upload host range [ptr, ptr+bytes) now and serve later calls whose weight
  * pointer falls inside it from HBM without fingerprinting.  Meant for the
  * `vault.load_npz` path (compiler/src/jit.rs:29836-29927), where the weight's
- * address is stable.  `wdtype` is DMC_W_BF16 or DMC_W_F32.  Returns a status. */
-int dmc_cuda_register_weight(int64_t ptr, int64_t bytes, int wdtype);
+ * address is stable.  `wdtype` is DMC_W_BF16 or DMC_W_F32.
+ * k, n > 0 say that the range is exactly one matrix in `layout` (bytes must equal k*n
+ * elements): a [k, n] matrix (DMC_LAYOUT_KN, the operand of `x @ w`) is then kept k-contiguous
+ * on the device, like a weight found by its fingerprint, and calls with that pointer and shape
+ * run the row-streaming kernel.  k = n = 0 registers an opaque range that is stored as the host
+ * has it and may be addressed at any offset (a model file holding many tensors).  Returns a status. */
+int dmc_cuda_register_weight(int64_t ptr, int64_t bytes, int64_t k, int64_t n, int layout, int wdtype);
 int dmc_cuda_unregister_weight(int64_t ptr);
 /* Number of resident weight buffers and their total bytes. */
 int64_t dmc_cuda_resident_count(void);
@@ -181,7 +199,8 @@ int dmc_cuda_gemv_bf16_noalloc(const void *dW, const float *dx, float *dy, int64
  * product sees x to 16 mantissa bits).  Needs k % 8 == 0.  Asynchronous on the context's stream. */
 int dmc_cuda_gemm_dev(const void *dW, const void *dX, float *dY, int64_t m, int64_t k, int64_t n, int xdtype);
 
-/* One device-resident GEMV of a benchmark step (arguments of dmc_cuda_gemv_dev). */
+/* One device-resident GEMV of a benchmark step (arguments of dmc_cuda_gemv_dev; `batch` > 1 runs that
+ * many m == 1 slices of a DMC_LAYOUT_KN weight at strides ls / rs elements, as the batched builtin does). */
 typedef struct dmc_gemv_item {
     const void *W;
     const float *x;
@@ -189,6 +208,7 @@ typedef struct dmc_gemv_item {
     int64_t m, k, n;
     int layout, wdtype, variant;
     int op; /* 0: dmc_cuda_gemv_dev; 1: dmc_cuda_gemm_dev with bf16 x; 2: dmc_cuda_gemm_dev with f32 x */
+    int64_t batch, ls, rs; /* batch <= 1: a single GEMV */
 } dmc_gemv_item;
 
 /* Device-timed benchmark: a step is the `count` GEMVs of `items` launched back
@@ -244,9 +264,23 @@ void dmc_cuda_shard_range(int64_t n, int rank, int world, int64_t *r0, int64_t *
 int dmc_cuda_shard_unique_id(uint8_t *out128);
 
 /* Join the communicator (collective: every rank calls it) and allocate the replicated output of
- * up to `max_n` floats.  world == 1 needs no id and no NCCL. */
+ * up to `max_n` floats.  world == 1 needs no id and no NCCL.  A failed init leaves nothing behind. */
 int dmc_cuda_shard_init(int rank, int world, const uint8_t *id128, int64_t max_n);
 void dmc_cuda_shard_shutdown(void);
+
+/* Which exchange a sharded GEMV of this size uses: 1 = fused into the kernel, 0 = ncclAllGather.  The
+ * answer depends only on facts that are equal on every rank (world size, whether EVERY rank mapped
+ * every peer -- agreed during init --, the "shard_fused" knob, k and n), so all ranks always take the
+ * same path; a rank whose slice is empty (n < world) still takes part in the chosen exchange.
+ * dmc_cuda_shard_path is the same rule from explicit facts (pure; no device). */
+int dmc_cuda_shard_uses_fused(int64_t k, int64_t n);
+int dmc_cuda_shard_path(int world, int peer_access_everywhere, int shard_fused, int64_t k, int64_t n);
+
+/* Self-test of the bounded device-side waits: runs the arrival check for an exchange that nobody writes,
+ * so every wait in it runs out after "wait_limit_us" and the call returns DMC_CUDA_ERR_TIMEOUT (sticky,
+ * like every failure).  Nothing faults or hangs; after dmc_cuda_clear_error() the context works as before.
+ * Needs dmc_cuda_shard_init with the fused exchange available (a world of one will do). */
+int dmc_cuda_shard_probe_timeout(int64_t n);
 
 /* y = W.x for W[n][k] (k contiguous) of which this rank holds rows dmc_cuda_shard_range(n, rank, world)
  * in `dW_shard` (device).  Runs the local GEMV and exchanges the f32 slices so that every rank holds
@@ -257,6 +291,9 @@ void dmc_cuda_shard_shutdown(void);
  * same order); dx must not alias dmc_cuda_shard_output() of the call before the previous one. */
 int dmc_cuda_shard_gemv(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype);
 float *dmc_cuda_shard_output(void);
+/* The result of the sharded GEMV before the last one (the fused exchange alternates between two
+ * buffers; with the NCCL exchange there is only one and this returns it).  Synchronises. */
+float *dmc_cuda_shard_output_previous(void);
 
 /* Device-timed benchmark of the call above on this rank: a step is one sharded GEMV per entry of
  * dW_shards (distinct copies of the shard, so the step's working set exceeds L2).  Returns this
@@ -310,11 +347,17 @@ const char *dmc_cuda_variant_name(int layout, int wdtype, int variant);
  *   tc_min_m          0    activation rows from which `@` goes to the tensor cores (0 = library default)
  *   tc_ksplit, tc_smem_kb                                tcgen05 GEMM: K splits, shared-memory ring budget
  *   shard_fused       -1   sharded GEMV: 1 = exchange fused into the kernel, 0 = ncclAllGather, -1 = fused
- *                          whenever the GPUs have peer access
- *   shard_exchange    3    protocol of the fused exchange, read by dmc_cuda_shard_init: 3 = epoch-tagged
- *                          elements + gather kernel, 2 = per-CTA arrival counters, 1 = flags by the last CTA
+ *                          whenever every pair of GPUs has peer access
  *   decode_fused      1    decode step: companions fused into the GEMVs / attention (0 = one kernel per op)
- *   shard_debug, decode_debug                            measurement only: leave parts of a step out */
+ *   overlap_independent 1  a GEMV that reads nothing a still-running kernel writes (and writes nothing one reads
+ *                          or writes) skips its dependency wait and overlaps its predecessors; 0 = every
+ *                          kernel waits for the one before it
+ *   wait_limit_us     0    bound of device-side waits on another rank, read by dmc_cuda_shard_init (0 = ~1 s);
+ *                          a wait that runs out makes the next synchronising call return DMC_CUDA_ERR_TIMEOUT
+ *   spin_sync         1    host-pointer builtins poll the stream instead of blocking on it
+ *   timing            0    one line per host-pointer call on stderr: microseconds spent on weights, staging and
+ *                          launch, waiting, readback, and the kernel's own time and GB/s (also DMC_CUDA_TIME=1;
+ *                          the counterpart of the reference's DMC_GPU_TIME, compiler/src/gpu.rs:45-96) */
 int dmc_cuda_set_param(const char *name, int64_t value);
 
 /* Kernels this library has launched since the context was created. */

@@ -272,7 +272,7 @@ def test_registered_weight_range():
     k, n = 512, 768
     rng = np.random.default_rng(10)
     blob = synth.bf16_weights(rng, (3 * k * n,))       # three layers in one vault buffer
-    assert lib.dmc_cuda_register_weight(blob.ctypes.data, blob.nbytes, backend.W_BF16) == 0
+    assert lib.dmc_cuda_register_weight(blob.ctypes.data, blob.nbytes, 0, 0, 0, backend.W_BF16) == 0      # opaque range
     before = lib.dmc_cuda_resident_count()
     x = synth.activations(rng, (1, k))
     for layer in range(3):
@@ -283,6 +283,112 @@ def test_registered_weight_range():
         assert_parity(out, oracle.gemm_bf16_fma(x, w.reshape(k, n)), TOL_BF16)
     assert lib.dmc_cuda_resident_count() == before      # served from the registered range, no new uploads
     assert lib.dmc_cuda_unregister_weight(blob.ctypes.data) == 0
+
+
+def test_registered_matrix_is_stored_k_contiguous():
+    """A registered [k, n] matrix (the vault-load hook with its shape) gets the same k-contiguous
+    residency as a weight found by fingerprint: one transpose at registration, then the row kernel."""
+    lib = dmc.load()
+    k, n = 4096, 1024
+    rng = np.random.default_rng(11)
+    w = synth.bf16_weights(rng, (k, n))
+    x = synth.activations(rng, (1, k))
+    before = lib.dmc_cuda_launch_count()
+    assert lib.dmc_cuda_register_weight(w.ctypes.data, w.nbytes, k, n, backend.LAYOUT_KN, backend.W_BF16) == 0
+    assert lib.dmc_cuda_launch_count() - before == 1, "one transpose kernel at registration"
+    resident = lib.dmc_cuda_resident_count()
+    assert_parity(gpu_bf16(x, w, 1, k, n), oracle.gemm_bf16_fma(x, w), TOL_BF16)
+    assert lib.dmc_cuda_launch_count() - before == 2 and lib.dmc_cuda_resident_count() == resident
+    # another view of the same bytes is served by content, not from the transposed copy
+    assert_parity(gpu_bf16(x[:, :2048], w.reshape(2048, 2048), 1, 2048, 2048),
+                  oracle.gemm_bf16_fma(x[:, :2048], w.reshape(2048, 2048)), TOL_BF16)
+    assert lib.dmc_cuda_unregister_weight(w.ctypes.data) == 0
+    assert lib.dmc_cuda_register_weight(w.ctypes.data, w.nbytes - 2, k, n, backend.LAYOUT_KN, backend.W_BF16) == 2   # not k*n elements
+    lib.dmc_cuda_clear_error()
+    lib.dmc_cuda_drop_resident()
+
+
+@pytest.mark.parametrize("m", [2, 3, 4, 5, 8, 9, 16])
+def test_small_batch_keeps_f32_rows_on_the_cuda_cores(m):
+    """x @ w' with a few f32 rows of x on a k-contiguous weight: up to 8 rows share every weight load
+    in the multi-row kernel with exact f32 activations (parity at the f32-order level, far inside 1e-2);
+    more rows go to the tensor cores."""
+    k, n = 4096, 4096
+    rng = np.random.default_rng(700 + m)
+    w = synth.bf16_weights(rng, (n, k))
+    x = synth.activations(rng, (m, k))
+    out = np.full((m, n), np.nan, F)
+    lib = dmc.load()
+    before = lib.dmc_cuda_launch_count()
+    dmc.matmul_bf16_gpu_nt(x, w, out, m, k, n)
+    dmc.matmul_bf16_gpu_nt(x, w, out, m, k, n)                  # the weight is resident now: count this call's launches
+    launches = (lib.dmc_cuda_launch_count() - before) // 2
+    ref = oracle.gemm_bf16_fma(x, np.ascontiguousarray(w.T))
+    err = assert_parity(out, ref, TOL_BF16, f"m={m}")
+    if m <= 8:
+        assert err < 1e-5, f"m={m}: the CUDA-core rows use exact f32 activations (got {err:.2e})"
+        assert launches == bin(m).count("1"), "rows taken 8, 4, 2 or 1 at a time, W streamed once per instance"
+
+
+def test_batched_slices_with_several_rows_run_on_the_gpu():
+    # compiler/src/gpu.rs:428-437: batch > 1 with m != 1 runs slice by slice; here on the GPU, not refused
+    lib = dmc.load()
+    m, k, n, batch = 3, 512, 256, 4
+    rng = np.random.default_rng(15)
+    l = synth.activations(rng, (batch, m, k))
+    r = synth.bf16_weights(rng, (batch, k, n))
+    out = np.full((batch, m, n), np.nan, F)
+    dmc.matmul_bf16_gpu_batched(l, r, out, m, k, n, batch, m * k, k * n)
+    for z in range(batch):
+        assert_parity(out[z], oracle.gemm_bf16_fma(l[z], r[z]), TOL_BF16, f"slice {z}")
+    assert not backend.matmul_selected(True, 0, m, k, n, batch)        # ... though the JIT gate never selects it
+    # whatever the predicate selects, the entry points accept
+    for (mm, kk, nn, bb) in [(1, 2560, 128, 8), (1, 128, 2560, 32), (1, 4096, 4096, 1), (1, 1000, 1000, 4)]:
+        if backend.matmul_selected(True, 0, mm, kk, nn, bb):
+            l2 = synth.activations(rng, (bb, mm, kk))
+            r2 = synth.bf16_weights(rng, (bb, kk, nn))
+            o2 = np.zeros((bb, mm, nn), F)
+            dmc.matmul_bf16_gpu_batched(l2, r2, o2, mm, kk, nn, bb, mm * kk, kk * nn)
+            assert lib.dmc_cuda_status() == 0
+            assert_parity(o2[bb - 1], oracle.gemm_bf16_fma(l2[bb - 1], r2[bb - 1]), TOL_BF16)
+
+
+def test_independent_gemvs_overlap_and_dependent_ones_do_not():
+    """A GEMV whose operands no running kernel touches skips its dependency wait; one that consumes
+    an earlier result must still see it.  Same numbers with the overlap on and off."""
+    lib = dmc.load()
+    k = n = 2048
+    rng = np.random.default_rng(16)
+    ws = [synth.bf16_weights(rng, (n, k)) for _ in range(4)]
+    x = synth.activations(rng, (k,)) 
+    dWs = [backend.DeviceBuffer.from_host(w) for w in ws]
+    dx = backend.DeviceBuffer.from_host(x)
+    dys = [backend.DeviceBuffer(n * 4) for _ in range(4)]
+    dchain = [backend.DeviceBuffer(n * 4) for _ in range(3)]
+    results = {}
+    for overlap in (1, 0):
+        lib.dmc_cuda_set_param(b"overlap_independent", overlap)
+        for rep in range(3):
+            for dW, dy in zip(dWs, dys):                           # four independent GEMVs of the same x
+                backend.gemv_dev(dW, dx, dy, 1, k, n, backend.LAYOUT_NK)
+            backend.gemv_dev(dWs[0], dx, dchain[0], 1, k, n, backend.LAYOUT_NK)          # a chain: each consumes the previous y
+            backend.gemv_dev(dWs[1], dchain[0], dchain[1], 1, k, n, backend.LAYOUT_NK)
+            backend.gemv_dev(dWs[2], dchain[1], dchain[2], 1, k, n, backend.LAYOUT_NK)
+            backend.gemv_dev(dWs[3], dx, dchain[0], 1, k, n, backend.LAYOUT_NK)          # overwrites what the chain's 2nd link read
+        backend.sync()
+        results[overlap] = [d.download(F, n) for d in dys + dchain]
+    lib.dmc_cuda_set_param(b"overlap_independent", 1)
+    for a, b in zip(results[1], results[0]):
+        assert np.array_equal(a, b), "overlapping launches changed a result"
+    xs = x.reshape(1, k)
+    for w, y in zip(ws, results[1][:4]):
+        assert_parity(y, oracle.gemm_bf16_fma(xs, np.ascontiguousarray(w.T)), TOL_BF16)
+    y0 = oracle.gemm_bf16_fma(xs, np.ascontiguousarray(ws[0].T))
+    y1 = oracle.gemm_bf16_fma(y0, np.ascontiguousarray(ws[1].T))
+    y2 = oracle.gemm_bf16_fma(y1, np.ascontiguousarray(ws[2].T))
+    assert_parity(results[1][5], y1, TOL_BF16, "second link")
+    assert_parity(results[1][6], y2, TOL_BF16, "third link")
+    assert_parity(results[1][4], oracle.gemm_bf16_fma(xs, np.ascontiguousarray(ws[3].T)), TOL_BF16, "the overwrite comes last")
 
 
 def test_f32_operand_is_not_cached_by_fingerprint():
@@ -384,7 +490,7 @@ def test_tma_ring_kernel(k, n, wdtype):
 
 
 def test_resident_kn_weight_is_stored_k_contiguous_once():
-    # a [k, n] weight the ring kernel can take is transposed on the device at upload; later calls reuse it
+    # a [k, n] weight the row-streaming kernel can take is transposed on the device at upload; later calls reuse it
     lib = dmc.load()
     lib.dmc_cuda_drop_resident()
     k, n = 4096, 1024

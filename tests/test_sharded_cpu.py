@@ -22,6 +22,26 @@ def test_shard_plan_covers_every_row_once():
     assert sharded.shard_range(65536, 3, 8) == (24576, 32768)
 
 
+def test_every_rank_chooses_the_same_exchange():
+    """The exchange (fused into the kernel, or NCCL) is chosen from facts that are equal on every
+    rank, never from a rank's own slice: with fewer rows than ranks some slices are empty, and a rank
+    that went the other way would leave its peers waiting for it."""
+    from demonic_b200 import _lib
+    lib = _lib.load()
+    for world in (2, 4, 8):
+        for n in (1, 3, world - 1, world, 65536):
+            for knob in (-1, 0, 1):
+                for peers_ok in (0, 1):
+                    want = lib.dmc_cuda_shard_path(world, peers_ok, knob, 8192, n)
+                    # the rule takes no rank and no slice, so it cannot differ between ranks; empty slices keep it
+                    empty = [r for r in range(world) if sharded.shard_range(n, r, world)[0] == sharded.shard_range(n, r, world)[1]]
+                    assert (n < world) == bool(empty)
+                    assert want == int(peers_ok and knob != 0 and n > 0)
+    assert lib.dmc_cuda_shard_path(1, 1, -1, 8192, 100) == 0        # a world of one exchanges nothing by default
+    assert lib.dmc_cuda_shard_path(1, 1, 1, 8192, 100) == 1         # ... unless asked (the single-GPU tests do)
+    assert lib.dmc_cuda_shard_path(8, 1, -1, 0, 100) == 0           # empty contraction: y is zero, nothing to exchange
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

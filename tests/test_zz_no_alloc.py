@@ -5,10 +5,9 @@ its own budgeted arena, or a decode loop that cannot take the device-wide stall 
 while other streams run.  For them one entry point keeps its split-K scratch in a fixed array
 inside the library.  This test drives it through the C ABI on device buffers the *caller*
 allocated, twice in a row (the second call finds the first call's leftovers in the shared array),
-and compares each result with the ordinary entry point's on the same inputs.
-
-Kept in a file that pytest collects last, so a run that stops at the first failure has already
-run everything else; it passes alone in a fresh process and after the other tests.
+and compares each result with the ordinary entry point's on the same inputs and with the CPU
+oracle, and checks that the free device memory is the same after the calls as before them.
+It passes alone in a fresh process and after the other tests.
 """
 import ctypes
 
@@ -16,6 +15,7 @@ import numpy as np
 import pytest
 
 import demonic_b200 as dmc
+import oracle
 from demonic_b200 import _lib, backend, synth
 from tests.parity import TOL_BF16, assert_parity
 
@@ -30,7 +30,14 @@ def cudart():
     rt.cudaStreamCreate.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
     rt.cudaStreamSynchronize.argtypes = [ctypes.c_void_p]
     rt.cudaStreamDestroy.argtypes = [ctypes.c_void_p]
+    rt.cudaMemGetInfo.argtypes = [ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
     return rt
+
+
+def free_device_bytes(rt) -> int:
+    free, total = ctypes.c_size_t(), ctypes.c_size_t()
+    assert rt.cudaMemGetInfo(ctypes.byref(free), ctypes.byref(total)) == 0
+    return free.value
 
 
 def test_noalloc_entry_matches_the_allocating_one_twice_in_a_row():
@@ -54,11 +61,19 @@ def test_noalloc_entry_matches_the_allocating_one_twice_in_a_row():
         want = dy_ref.download(F, n)
         lib.dmc_cuda_memset(dy_new.ptr, 0xFF, n * 4)
         backend.sync()
+        free_before = free_device_bytes(rt)
         rc = lib.dmc_cuda_gemv_bf16_noalloc(dW.ptr, dx.ptr, dy_new.ptr, k, n, stream)
         assert rc == 0, lib.dmc_cuda_last_error().decode()
         assert rt.cudaStreamSynchronize(stream) == 0
+        if call == 0:
+            # the first call on a device makes the CUDA runtime load this kernel's part of the library image,
+            # which includes the fixed scratch array: a one-time cost of the image, a few MiB, not an allocation
+            assert free_before - free_device_bytes(rt) <= 32 << 20
+        else:
+            assert free_device_bytes(rt) == free_before, "the entry point allocated (or freed) device memory"
         got = dy_new.download(F, n)
-        assert_parity(got, want, TOL_BF16, f"call {call + 1}")
+        assert_parity(got, want, TOL_BF16, f"call {call + 1} vs the allocating entry point")
+        assert_parity(got, oracle.gemm_bf16_fma(x.reshape(1, k), w), TOL_BF16, f"call {call + 1} vs the CPU oracle")
     # a second shape through the same array (fewer K slices, ragged last column block)
     k2, n2 = 1000, 264
     w2 = synth.bf16_weights(rng, (k2, n2))
@@ -70,6 +85,7 @@ def test_noalloc_entry_matches_the_allocating_one_twice_in_a_row():
     assert lib.dmc_cuda_gemv_bf16_noalloc(dW2.ptr, dx2.ptr, dy_new.ptr, k2, n2, stream) == 0
     assert rt.cudaStreamSynchronize(stream) == 0
     assert_parity(dy_new.download(F, n2), want2, TOL_BF16, "second shape")
+    assert_parity(dy_new.download(F, n2), oracle.gemm_bf16_fma(x2.reshape(1, k2), w2), TOL_BF16, "second shape vs the CPU oracle")
     assert rt.cudaStreamDestroy(stream) == 0
 
 
