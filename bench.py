@@ -495,6 +495,9 @@ def run_case(args) -> None:
         return
     rows, cols = (int(t) for t in args.case.split("x"))
     rng = np.random.default_rng(synth.DEFAULT_SEED)
+    if args.timeline:
+        run_timeline(args, lib, backend, synth, rows, cols, rng)
+        return
     w = synth.bf16_weights(rng, (rows, cols))
     x = synth.bf16_weights(rng, (args.m, cols)) if args.op == 1 else synth.activations(rng, (args.m, cols))
     copies = max(2, -(-(args.mib << 20) // w.nbytes))
@@ -507,6 +510,41 @@ def run_case(args) -> None:
     b = synth.gemv_bytes(rows, cols, m=args.m)
     print(f"{args.case} {args.layout} m={args.m} op={args.op} variant={args.variant}: {us:.2f} us/launch, {b / us / 1e3:.0f} GB/s "
           f"(algorithmic bytes {b})")
+
+
+def run_timeline(args, lib, backend, synth, rows, cols, rng) -> None:
+    """Where the time between two GEMVs of a chain goes: per-CTA time stamps of `--launches` back-to-back
+    GEMVs of one shape (dmc_cuda_timeline), once with every GEMV waiting for its predecessor and once with
+    none waiting, reported relative to the moment the previous GEMV's last CTA finished."""
+    import ctypes as C
+    w = synth.bf16_weights(rng, (rows, cols))
+    count = max(args.launches, 6)
+    bufs = [backend.DeviceBuffer.from_host(w) for _ in range(count)]
+    dx = backend.DeviceBuffer.from_host(synth.activations(rng, (cols,)))
+    dy = backend.DeviceBuffer(rows * 4)
+    ptrs = (C.c_void_p * count)(*[b.ptr for b in bufs])
+    cap = count * 1024 * 8
+    stamps = np.zeros(cap, np.uint64)
+    b = synth.gemv_bytes(rows, cols)
+    names = ["entry", "wait returned", "x staged", "first group done", "last group done"]
+    for dependent in (1, 0):
+        grid = lib.dmc_cuda_timeline(C.cast(ptrs, C.c_void_p), count, dx.ptr, dy.ptr, cols, rows, dependent,
+                                     stamps.ctypes.data_as(C.c_void_p), cap)
+        assert grid > 0, lib.dmc_cuda_last_error().decode()
+        st = stamps[:count * grid * 8].reshape(count, grid, 8).astype(np.int64)
+        ends = st[:, :, 4].max(axis=1)
+        periods = np.diff(ends)[2:]
+        print(f"{args.case} {'every GEMV waits for its predecessor' if dependent else 'no GEMV waits'}: grid {grid} CTAs, "
+              f"period {np.median(periods) / 1e3:.2f} us per GEMV = {b / np.median(periods):.0f} GB/s "
+              f"(min {periods.min() / 1e3:.2f}, max {periods.max() / 1e3:.2f} over {len(periods)} links)")
+        print("  ns after the previous GEMV's last CTA finished: min / median / max over the CTAs, median over the links")
+        rel = st[3:, :, :5] - ends[2:-1, None, None]
+        for j, name in enumerate(names):
+            col = rel[:, :, j]
+            print(f"    {name:18s} {int(np.median(col.min(axis=1))):7d} / {int(np.median(np.median(col, axis=1))):7d} / {int(np.median(col.max(axis=1))):7d}")
+        sms = st[3, :, 5]
+        per_sm = np.bincount(sms.astype(int))
+        print(f"  CTAs per SM in one launch: {dict(zip(*np.unique(per_sm[per_sm > 0], return_counts=True)))}")
 
 
 def main() -> None:
@@ -524,6 +562,7 @@ def main() -> None:
     ap.add_argument("--op", type=int, default=0, help="--case: 0 GEMV kernels, 1 tcgen05 GEMM (bf16 x), 2 tcgen05 GEMM (f32 x)")
     ap.add_argument("--decode", type=int, default=0, help="--case: run this many decode steps of the benchmark model instead")
     ap.add_argument("--param", action="append", default=[], help="--case: tuning knob name=value")
+    ap.add_argument("--timeline", action="store_true", help="--case: per-CTA time stamps of a chain of GEMVs of this shape")
     args = ap.parse_args()
     if args.case or args.decode:
         run_case(args)

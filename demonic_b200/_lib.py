@@ -63,6 +63,7 @@ SIGNATURES = {
     "dmc_npz_locate": (C.c_int, [C.c_char_p, C.c_char_p, VP]),
     "dmc_cuda_load_npz": (C.c_int, [C.c_char_p, C.c_char_p, I64, I64, C.c_int, C.c_int, C.c_int, I64, C.POINTER(VP),
                                     C.POINTER(I64)]),
+    "dmc_cuda_timeline": (C.c_int, [VP, C.c_int, VP, VP, I64, I64, C.c_int, VP, I64]),
     "dmc_cuda_bench_items": (C.c_double, [VP, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_variant_count": (C.c_int, [C.c_int, C.c_int]),
     "dmc_cuda_variant_name": (C.c_char_p, [C.c_int, C.c_int, C.c_int]),

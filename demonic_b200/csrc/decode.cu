@@ -26,7 +26,8 @@ struct Decoder {
     float *gf = nullptr, *rope_cos = nullptr, *rope_sin = nullptr;
     float *h2 = nullptr;        // second residual-stream buffer (the fused RMSNorm ping-pongs between h and h2)
     unsigned *attn_cnt = nullptr;
-    float *am_val = nullptr;    // argmax per-CTA candidates
+    unsigned long long *am_key = nullptr;  // arg-max key the lm-head GEMV leaves (fused arrangement)
+    float *am_val = nullptr;    // argmax per-CTA candidates (unfused arrangement)
     int *am_idx = nullptr;
     unsigned *am_cnt = nullptr;
     int fused = 1;              // 1: RMSNorm / SwiGLU fused into the GEMVs' staging, RoPE + append + combine into attention
@@ -74,7 +75,8 @@ int enqueue_step_fused(Decoder &d, cudaStream_t s) {
     const int D = c.d_model, H = c.heads, F = c.ffn, V = c.vocab, cap = c.max_len;
     int rc;
     float *hin = d.h, *hout = d.h2;
-    if ((rc = launch_small(embed_kernel, dim3(8), dim3(256), s, (const uint16_t *)d.embed, V, D, (const int *)d.d_token, hin)))
+    if ((rc = launch_small(embed_kernel, dim3(8), dim3(256), s, (const uint16_t *)d.embed, V, D, (const int *)d.d_token, hin,
+                           d.am_key)))
         return rc;
     const float *carry = nullptr;
     const int chunk = (cap + d.splits - 1) / d.splits;
@@ -95,8 +97,11 @@ int enqueue_step_fused(Decoder &d, cudaStream_t s) {
         if ((rc = gemv_pro(L.wd, d.gu, d.d2, F, D, 2, nullptr, nullptr, nullptr, 0.0f, s))) return rc;
         carry = d.d2;
     }
-    if ((rc = gemv_pro(d.lm_head, hin, d.logits, D, V, 1, carry, d.gf, nullptr, c.eps, s))) return rc;
-    return launch_small(argmax_kernel, dim3(64), dim3(256), s, (const float *)d.logits, V, d.d_next, d.am_val, d.am_idx, d.am_cnt);
+    // logits = lm_head . rms_norm(h + carry), and their arg-max in the same kernel
+    ctx().amax = d.am_key;
+    rc = gemv_pro(d.lm_head, hin, d.logits, D, V, 1, carry, d.gf, nullptr, c.eps, s);
+    ctx().amax = nullptr;
+    return rc;
 }
 
 // The unfused sequence (9 launches per layer), kept as the reference arrangement of the same math.
@@ -104,7 +109,8 @@ int enqueue_step_plain(Decoder &d, cudaStream_t s) {
     const dmc_decoder_config &c = d.cfg;
     const int D = c.d_model, H = c.heads, hd = c.head_dim, F = c.ffn, V = c.vocab, cap = c.max_len;
     int rc;
-    if ((rc = launch_small(embed_kernel, dim3(8), dim3(256), s, (const uint16_t *)d.embed, V, D, (const int *)d.d_token, d.h)))
+    if ((rc = launch_small(embed_kernel, dim3(8), dim3(256), s, (const uint16_t *)d.embed, V, D, (const int *)d.d_token, d.h,
+                           (unsigned long long *)nullptr)))
         return rc;
     const float *carry = nullptr;  // residual branch output waiting to be added to h
     const int chunk = (cap + d.splits - 1) / d.splits;
@@ -194,7 +200,7 @@ extern "C" int dmc_decoder_create(const dmc_decoder_config *cfg, void **out) {
          dalloc(&d->ao, D) || dalloc(&d->d1, D) || dalloc(&d->gu, 2 * F) || dalloc(&d->act, F) || dalloc(&d->d2, D) ||
          dalloc(&d->logits, V) || dalloc(&d->part, H * (size_t)d->splits * (hd + 2)) || dalloc(&d->d_token, 1) ||
          dalloc(&d->d_pos, 1) || dalloc(&d->d_next, 1) || dalloc(&d->h2, D) || dalloc(&d->attn_cnt, H) ||
-         dalloc(&d->am_val, 64) || dalloc(&d->am_idx, 64) || dalloc(&d->am_cnt, 1);
+         dalloc(&d->am_val, 64) || dalloc(&d->am_idx, 64) || dalloc(&d->am_cnt, 1) || dalloc(&d->am_key, 1);
     d->fused = tuning().decode_fused;
     for (Layer &L : d->layers)
         rc = rc || dalloc(&L.wqkv, 3 * D * D) || dalloc(&L.wo, D * D) || dalloc(&L.wgu, 2 * F * D) || dalloc(&L.wd, D * F) ||
@@ -245,9 +251,13 @@ extern "C" int dmc_decoder_step(void *dec, int token, int pos, int *next_token, 
     DMC_CUDA_TRY(cudaGraphLaunch(d->exec, s));
     ctx().launches += d->launches_per_step;
     int next = 0;
-    DMC_CUDA_TRY(cudaMemcpyAsync(&next, d->d_next, 4, cudaMemcpyDeviceToHost, s));
+    unsigned long long key = 0ull;
+    if (d->fused) DMC_CUDA_TRY(cudaMemcpyAsync(&key, d->am_key, 8, cudaMemcpyDeviceToHost, s));
+    else DMC_CUDA_TRY(cudaMemcpyAsync(&next, d->d_next, 4, cudaMemcpyDeviceToHost, s));
     if (logits_out) DMC_CUDA_TRY(cudaMemcpyAsync(logits_out, d->logits, (size_t)d->cfg.vocab * 4, cudaMemcpyDeviceToHost, s));
     DMC_CUDA_TRY(cudaStreamSynchronize(s));
+    stream_drained();
+    if (d->fused) next = key ? (int)(0xFFFFFFFFu - (unsigned)(key & 0xFFFFFFFFull)) : 0;  // low half: 0xFFFFFFFF - row
     if (next_token) *next_token = next;
     return dmc::status();
 }
@@ -300,7 +310,8 @@ extern "C" void dmc_decoder_destroy(void *dec) {
     if (d->exec) cudaGraphExecDestroy(d->exec);
     if (d->graph) cudaGraphDestroy(d->graph);
     void *singles[] = {d->embed, d->lm_head, d->gf, d->rope_cos, d->rope_sin, d->h, d->xn, d->qkv, d->ao, d->d1, d->gu,
-                       d->act, d->d2, d->logits, d->part, d->d_token, d->d_pos, d->d_next, d->h2, d->attn_cnt, d->am_val, d->am_idx, d->am_cnt};
+                       d->act, d->d2, d->logits, d->part, d->d_token, d->d_pos, d->d_next, d->h2, d->attn_cnt, d->am_val, d->am_idx, d->am_cnt,
+                       d->am_key};
     for (void *p : singles)
         if (p) cudaFree(p);
     for (Layer &L : d->layers) {

@@ -36,8 +36,9 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
 
 // h[d] = widen(vocab[clamp(id)][d])
 __global__ void embed_kernel(const uint16_t *__restrict__ vocab, int V, int D, const int *__restrict__ id_ptr,
-                             float *__restrict__ h) {
+                             float *__restrict__ h, unsigned long long *__restrict__ amax_key) {
     griddep_wait();
+    if (amax_key && blockIdx.x == 0 && threadIdx.x == 0) *amax_key = 0ull;  // re-armed for this step's lm-head
     int id = *id_ptr;
     id = id < 0 ? 0 : (id > V - 1 ? V - 1 : id);
     for (int d = blockIdx.x * blockDim.x + threadIdx.x; d < D; d += gridDim.x * blockDim.x)
@@ -188,13 +189,14 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float *__restrict
     const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
     const int t0 = z * chunk;
     constexpr int KU = 8;  // keys in flight per warp: the loop is bound by memory latency, not by arithmetic
-    griddep_wait();
+    // `pos` is written by a copy that completed before the first kernel of the step started, and the
+    // cached rows below `pos` by earlier steps: neither depends on the kernel before this one, so both
+    // are read BEFORE the dependency wait and the whole cache of the layer is in flight while the qkv
+    // projection is still finishing.  (The row at `pos` is the one this launch appends: it is taken
+    // from shared memory below, never from the cache.)
     const int pos = *pos_ptr, len = pos + 1;
     const int t1 = min(len, t0 + chunk);
     const bool owns_new = pos >= t0 && pos < t0 + chunk;
-    // The first batch of cached keys/values does not depend on q: request it before the RoPE section, so
-    // the two memory latencies overlap.  (The row at `pos` is the one this launch appends: it is taken
-    // from shared memory below, never from the cache.)
     float4 k4[KU], v4[KU];
     auto load_batch = [&](int tb) {
 #pragma unroll
@@ -209,8 +211,9 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float *__restrict
         }
     };
     load_batch(t0 + warp);
+    const float c = cs[(size_t)pos * (HD / 2) + (d >> 1)], s = sn[(size_t)pos * (HD / 2) + (d >> 1)];  // constant tables
+    griddep_wait();  // q, k, v of this token come from the projection before this kernel
     {   // RoPE, pairs (2i, 2i+1): thread d holds element d and reads its partner
-        const float c = cs[(size_t)pos * (HD / 2) + (d >> 1)], s = sn[(size_t)pos * (HD / 2) + (d >> 1)];
         const float *q = qkv + (size_t)h * HD, *k = qkv + (size_t)(H + h) * HD, *v = qkv + (size_t)(2 * H + h) * HD;
         const float qa = q[d & ~1], qb = q[d | 1];
         qs[d] = (d & 1) ? qa * s + qb * c : qa * c - qb * s;

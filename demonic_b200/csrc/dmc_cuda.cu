@@ -143,9 +143,9 @@ int ensure_init() {
 
 // ---- staging ---------------------------------------------------------------------
 
-// Wait for the stream.  The host-pointer builtins are latency-bound (a 10 us kernel between two
-// small copies), and a blocking synchronise adds a thread wake-up to every call: "spin_sync" polls
-// the stream instead, at the price of a busy host core while the GPU works.
+// Wait for the stream.  "spin_sync" polls cudaStreamQuery instead of blocking in
+// cudaStreamSynchronize; measured on B200 it is slower (49 vs 35 us per 4096x4096 call: the polling
+// competes with the driver's own completion handling), so it is off by default.
 static cudaError_t stream_wait(cudaStream_t s) {
     if (!g_tuning.spin_sync) return cudaStreamSynchronize(s);
     for (;;) {
@@ -363,6 +363,11 @@ static int run_host_call_locked(const HostCall &h) {
         y_base = (c.y_off + 255) & ~(size_t)255;
     }
 
+    // x first: its copy to the device runs while the host looks the weight up (the content
+    // fingerprint touches 256 cache lines spread over the whole weight, ~5 us)
+    memcpy(c.h_x + x_base, h.l, x_elems * 4);
+    DMC_CUDA_TRY(cudaMemcpyAsync(c.d_x + x_base, c.h_x + x_base, x_elems * 4, cudaMemcpyHostToDevice, c.stream));
+
     // weights: resident, or (f32 operand that may change between calls) uploaded now
     void *dW = nullptr;
     int layout = h.layout;
@@ -405,12 +410,12 @@ static int run_host_call_locked(const HostCall &h) {
     }
     const double t1 = timing ? now_us() : 0.0;
 
-    memcpy(c.h_x + x_base, h.l, x_elems * 4);
-    DMC_CUDA_TRY(cudaMemcpyAsync(c.d_x + x_base, c.h_x + x_base, x_elems * 4, cudaMemcpyHostToDevice, c.stream));
-    // Outputs are small (4n bytes): by default the kernel stores them straight into the pinned host
-    // mirror (device-visible through unified addressing), which saves the device->host copy and its
-    // launch latency on every call; "zero_copy_y" = 0 goes through the device buffer and a copy.
-    const bool zc = g_tuning.zero_copy_y != 0;
+    // Small outputs (up to 64 KiB) are stored by the kernel straight into the pinned host mirror
+    // (device-visible through unified addressing), which saves the device->host copy and its launch
+    // latency (measured: 35 vs 39 us per 4096x4096 call); larger ones (an lm-head's 600 KB of logits)
+    // would cross PCIe four bytes at a time, so they go through the device buffer and one copy.
+    // "zero_copy_y" = 0 always copies.
+    const bool zc = g_tuning.zero_copy_y != 0 && y_elems * 4 <= (64u << 10);
     float *y_target = zc ? (float *)(c.h_y + y_base) : (float *)(c.d_y + y_base);
     if (timing) {
         if (!c.ev0) {
@@ -813,6 +818,13 @@ extern "C" double dmc_cuda_bench_items(const dmc_gemv_item *items, int count, in
     if (e0) cudaEventDestroy(e0);
     if (e1) cudaEventDestroy(e1);
     return dmc::status() ? -1.0 : us;
+}
+
+extern "C" int dmc_cuda_timeline(const void *const *dWs, int count, const float *dx, float *dy, int64_t k, int64_t n,
+                                 int dependent, unsigned long long *stamps_out, int64_t stamps_cap_words) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status() || ensure_init()) return -dmc::status();
+    return timeline_nk(dWs, count, dx, dy, k, n, dependent, stamps_out, stamps_cap_words, ctx().stream);
 }
 
 extern "C" int64_t dmc_cuda_launch_count(void) { return ctx().launches; }

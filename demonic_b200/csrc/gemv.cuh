@@ -45,7 +45,28 @@ struct GemvArgs {
     const float *pro_add, *pro_g;
     float *pro_hout;
     float pro_eps;
+    // NK kernel, M == 1: if non-null, the arg-max of y is folded into the kernel.  The word receives,
+    // by atomic maximum, (order-preserving bits of the value) << 32 | (0xFFFFFFFF - row): the greatest
+    // value wins and, among equal values, the lowest row -- the reference's first strict maximum
+    // (compiler/src/interp.rs:13529-13538).  The caller zeroes it beforehand.
+    unsigned long long *amax;
+    // Time-line instantiation only (STAMP = true): per CTA {kernel entry, wait returned, x staged,
+    // first row group done, last row group done} in globaltimer nanoseconds, plus the SM id.
+    unsigned long long *stamps;
 };
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Order-preserving map f32 -> u32 (greater float <=> greater unsigned) and the packed arg-max key.
+__device__ __forceinline__ unsigned long long amax_key(float v, int row) {
+    const unsigned u = __float_as_uint(v);
+    const unsigned ord = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)ord << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)row);
+}
 
 // ---- small device helpers ---------------------------------------------------
 
@@ -310,7 +331,9 @@ __global__ void __launch_bounds__(TK * 32) dmc_wcols_any_kernel(const GemvArgs a
 // SMs x resident CTAs, every CTA with the same share of the rows.
 // Needs K % EPV == 0 and a 16-byte aligned W.  Dynamic shared memory: M rows of
 // K floats, each rounded up to a multiple of 256 floats.
-template <int WARPS, int R, int U, int M, typename WT>
+// STAMP = true is the same kernel with five time stamps per CTA (GemvArgs::stamps), used only by the
+// time-line measurement; the product instantiations carry none of it.
+template <int WARPS, int R, int U, int M, typename WT, bool STAMP = false>
 __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a) {
     constexpr int EPV = VecOf<WT>::EPV;
     constexpr int THREADS = WARPS * 32;
@@ -398,6 +421,8 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
         }
     };
 
+    unsigned long long t_entry = 0, t_wait = 0, t_x = 0, t_first = 0;
+    if (STAMP && threadIdx.x == 0) t_entry = globaltimer_ns();
     griddep_launch_dependents();
     int g = g0 + warp;
     if (g < g1) load_w(g * R, lane);  // weights depend on no earlier kernel: first loads go out before the wait
@@ -411,6 +436,7 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
             reinterpret_cast<unsigned *>(&s_peer)[i] = __ldg(reinterpret_cast<const unsigned *>(a.peer) + i);
     }
     if (!a.nowait) griddep_wait();
+    if (STAMP && threadIdx.x == 0) t_wait = globaltimer_ns();
     // after the wait: an earlier kernel (the end of the previous batch) is what advances the epoch word
     const PeerOut *peer = a.peer ? &s_peer : nullptr;
     if (a.peer) __syncthreads();  // the descriptor copy is complete
@@ -478,7 +504,9 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
         }
         __syncthreads();
     }
+    if (STAMP && threadIdx.x == 0) t_x = globaltimer_ns();
 
+    unsigned long long best = 0ull;  // arg-max epilogue: this warp's best (value, row) so far
     bool first = true;  // the warp's first row group: chunk 0 is already in registers
     for (; g < g1; g += WARPS) {
         const int row0 = g * R;
@@ -508,11 +536,36 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
                 } else if (lane == 0 && row < N) {
                     a.y[(size_t)m * N + row] = s;
                 }
+                if (M == 1 && a.amax && row < N && s == s) {  // (a NaN is never a maximum)
+                    const unsigned long long key = amax_key(s, row);
+                    best = key > best ? key : best;
+                }
             }
         }
         // The R rows of a warp are adjacent, so lanes 0..R-1 store them together: one R*8-byte write per
         // replica instead of R separate ones (fewer, larger NVLink packets).
         if (M == 1 && peer && lane < R && row0 + lane < N) peer_store(peer, epoch, a.yoff + row0 + lane, mine);
+        if (STAMP && threadIdx.x == 0 && t_first == 0) t_first = globaltimer_ns();
+    }
+    if (STAMP) {
+        __syncthreads();  // every warp of the CTA has finished its rows
+        if (threadIdx.x == 0) {
+            unsigned smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            unsigned long long *st = a.stamps + (size_t)blockIdx.x * 8;
+            st[0] = t_entry, st[1] = t_wait, st[2] = t_x, st[3] = t_first, st[4] = globaltimer_ns(), st[5] = smid;
+        }
+    }
+    if (M == 1 && a.amax) {  // one atomic per CTA
+        __shared__ unsigned long long s_best[WARPS];
+        if (lane == 0) s_best[warp] = best;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned long long b = s_best[0];
+#pragma unroll
+            for (int w2 = 1; w2 < WARPS; ++w2) b = s_best[w2] > b ? s_best[w2] : b;
+            if (b) atomicMax(a.amax, b);
+        }
     }
 }
 

@@ -387,6 +387,7 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
     a.pro_g = c.pro_g;
     a.pro_hout = c.pro_hout;
     a.pro_eps = c.pro_eps;
+    a.amax = m == 1 ? c.amax : nullptr;
     // rows of x are taken 8, 4, 2 or 1 at a time; every instance streams W once for its rows
     for (int64_t m0 = 0; m0 < m;) {
         const int64_t left = m - m0;
@@ -419,7 +420,7 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
         // May this launch overlap what is still running?  Only if nothing it reads is being written
         // and nothing it writes is being read or written.
         const size_t xbytes = (size_t)M * k * 4 * (a.pro == 2 ? 2 : 1), ybytes = (size_t)M * n * 4, hbytes = (size_t)k * 4;
-        const bool conflict = a.peer || !tuning().overlap_independent || c.untracked_inflight ||
+        const bool conflict = a.peer || a.amax || !tuning().overlap_independent || c.untracked_inflight ||
                               c.inflight_reads.size() + c.inflight_writes.size() > kMaxTrackedRanges ||
                               overlaps(c.inflight_writes, a.x, xbytes) || overlaps(c.inflight_writes, a.pro_add, hbytes) ||
                               overlaps(c.inflight_writes, a.y, ybytes) || overlaps(c.inflight_reads, a.y, ybytes) ||
@@ -439,6 +440,51 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
 }
 
 }  // namespace
+
+// Time line of a chain of `count` bf16 GEMVs of one shape (W[n][k] copies in dWs), launched back to
+// back in one CUDA graph with the default kernel configuration in its stamped instantiation.
+// `dependent` != 0: every GEMV waits for its predecessor (as if it consumed its output); 0: none waits.
+// stamps_out receives [count][grid][8] words (see GemvArgs::stamps); returns the grid size, < 0 on error.
+int timeline_nk(const void *const *dWs, int count, const float *dx, float *dy, int64_t k, int64_t n, int dependent,
+                unsigned long long *stamps_out, int64_t stamps_cap_words, cudaStream_t s) {
+    Context &c = ctx();
+    const size_t xrow = (size_t)((k + 255) / 256 * 256) * sizeof(float);
+    if (k % 8 || xrow > kNkMaxSmem || count < 1)
+        return -fail(DMC_CUDA_ERR_UNSUPPORTED, "timeline: needs k %% 8 == 0, a row of x that fits shared memory, count >= 1");
+    const void *fn = (const void *)dmc_wrows_kernel<8, 2, 8, 1, uint16_t, true>;
+    DMC_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNkMaxSmem));
+    const int64_t grid = nk_grid(n, 8, 2, c.sm_count, 2);
+    if ((int64_t)count * grid * 8 > stamps_cap_words) return -fail(DMC_CUDA_ERR_BAD_ARG, "timeline: stamp buffer too small");
+    unsigned long long *d_st = nullptr;
+    const size_t bytes = (size_t)count * grid * 8 * sizeof(unsigned long long);
+    DMC_CUDA_TRY(dmc_malloc((void **)&d_st, bytes));
+    DMC_CUDA_TRY(cudaStreamSynchronize(s));
+    stream_drained();
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int rc = DMC_CUDA_OK;
+    cudaError_t e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal);
+    for (int i = 0; i < count && e == cudaSuccess && rc == DMC_CUDA_OK; ++i) {
+        GemvArgs a = {};
+        a.W = dWs[i], a.x = dx, a.y = dy, a.K = (int)k, a.N = (int)n, a.ksplit = 1;
+        a.nowait = dependent ? 0 : 1;
+        a.stamps = d_st + (size_t)i * grid * 8;
+        void *params[] = {&a};
+        rc = launch_ex(fn, dim3((unsigned)grid), dim3(256), xrow, s, params, kLaunchTracked);
+    }
+    if (e == cudaSuccess) e = cudaStreamEndCapture(s, &graph);
+    stream_drained();
+    if (e == cudaSuccess && rc == DMC_CUDA_OK) e = cudaGraphInstantiate(&exec, graph, 0);
+    for (int rep = 0; rep < 4 && e == cudaSuccess && rc == DMC_CUDA_OK; ++rep) e = cudaGraphLaunch(exec, s);  // the last replay's stamps stay
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess) e = cudaMemcpy(stamps_out, d_st, bytes, cudaMemcpyDeviceToHost);
+    if (exec) cudaGraphExecDestroy(exec);
+    if (graph) cudaGraphDestroy(graph);
+    cudaFree(d_st);
+    if (rc) return -rc;
+    if (e != cudaSuccess) return -fail(DMC_CUDA_ERR_CUDA, "timeline: %s", cudaGetErrorString(e));
+    return (int)grid;
+}
 
 bool nk_fast_eligible(int64_t k, int64_t n, int wdtype) {
     const int epv = wdtype == DMC_W_BF16 ? 8 : 4;

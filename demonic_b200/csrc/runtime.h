@@ -95,6 +95,7 @@ struct Context {
     const float *pro_add = nullptr, *pro_g = nullptr;
     float *pro_hout = nullptr;
     float pro_eps = 0.0f;
+    unsigned long long *amax = nullptr;  // arg-max epilogue of the NK kernel (GemvArgs::amax)
 
     // pinned staging ring of the weight ingest, allocated on first use
     unsigned char *ingest_ring = nullptr;
@@ -122,7 +123,7 @@ struct Tuning {
     int overlap_independent = 1;  // GEMVs that touch nothing a running kernel touches skip their dependency wait
     int wait_limit_us = 0;  // bound of the device-side waits on another rank, microseconds (0 = about one second)
     int timing = 0;         // per-call phase timing printed to stderr (also DMC_CUDA_TIME=1)
-    int spin_sync = 1;      // host-pointer entry points poll the stream instead of blocking on it
+    int spin_sync = 0;      // host-pointer entry points poll the stream instead of blocking on it
 };
 
 Context &ctx();
@@ -171,6 +172,10 @@ cudaError_t dmc_malloc_host(void **p, size_t bytes);
 bool inject_failure(const char *what);
 // Grow the context's split-K scratch (partials in bytes, arrival counters in elements).
 int ensure_scratch(size_t partial_bytes, size_t ncounters);
+
+// Time line of a chain of GEMVs (gemv_launch.cu).
+int timeline_nk(const void *const *dWs, int count, const float *dx, float *dy, int64_t k, int64_t n, int dependent,
+                unsigned long long *stamps_out, int64_t stamps_cap_words, cudaStream_t s);
 
 // tcgen05 GEMM: Y[m][n] = X @ W' with W [n][k] bf16 (k contiguous) and X bf16 or f32.
 bool gemm_tc_eligible(int64_t m, int64_t k, int64_t n, const void *dW, const void *dX);

@@ -219,6 +219,17 @@ typedef struct dmc_gemv_item {
  * replayed.  Returns microseconds per step (< 0 on error). */
 double dmc_cuda_bench_items(const dmc_gemv_item *items, int count, int steps, int warmup, int use_graph);
 
+/* Time line of a chain of `count` bf16 GEMVs y = W.x of one shape (W[n][k] copies in dWs, all on the device),
+ * replayed from one CUDA graph with the default row-streaming kernel in an instantiation that records, per
+ * CTA, when it entered, when its dependency wait returned, when x was staged, when its first and its last row
+ * group were done (globaltimer nanoseconds) and on which SM it ran.  dependent != 0: every GEMV waits for
+ * its predecessor; 0: none does.  stamps_out receives [count][grid][8] words {entry, wait, x, first, end, sm,
+ * 0, 0}.  Returns the grid size (> 0), or minus a status code.  A measurement aid: it answers where the time
+ * between two dependent kernels goes, the way the reference documents its per-dispatch ramp
+ * (compiler/src/gpu.rs:23-30). */
+int dmc_cuda_timeline(const void *const *dWs, int count, const float *dx, float *dy, int64_t k, int64_t n, int dependent,
+                      unsigned long long *stamps_out, int64_t stamps_cap_words);
+
 /* ---- weight ingest ---------------------------------------------------------------------------
  * Replaces the host side of `vault.load_npz[bf16, [K, N]](path, key = "w")`
  * (dmc_vault_load_npz, compiler/src/jit.rs:29836-29927: zip entry `<key>.npy` or `<key>`, NPY v1/v2
