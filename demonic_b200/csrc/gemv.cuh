@@ -183,15 +183,21 @@ __device__ __forceinline__ void splitk_finish(const GemvArgs &a, int z, int grou
 // shared memory; CTA partials of a split K meet in `partial` (splitk_finish).
 // grid.x = colblocks * batch, grid.y = ksplit.  Needs N % EPV == 0, rs % EPV == 0
 // and a 16-byte aligned W.
-template <int TK, int U, int V, int M, typename WT>
+// NR > 1 is the form for narrow matrices (per-head projections with n = 128 or 64): a warp-wide load
+// covers NR consecutive k rows of 32/NR vectors each instead of one row of 32, so no lane idles; the NR
+// partial rows meet by shuffle at the end.
+template <int TK, int U, int V, int M, typename WT, int NR = 1>
 __global__ void __launch_bounds__(TK * 32) dmc_wcols_kernel(const GemvArgs a) {
     constexpr int EPV = VecOf<WT>::EPV;
-    constexpr int CW = 32 * V * EPV;
+    constexpr int LPR = 32 / NR;           // lanes per k row
+    constexpr int CW = LPR * V * EPV;
     constexpr int THREADS = TK * 32;
+    static_assert(NR == 1 || NR == 2 || NR == 4, "rows per warp-wide load");
     __shared__ __align__(16) float red[TK][CW];
     __shared__ int s_last;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lcol = lane % LPR, sub = lane / LPR;  // position within a k row, and which of the NR rows
     const int cb = blockIdx.x % a.colblocks, z = blockIdx.x / a.colblocks;
     const int K = a.K, N = a.N;
     const WT *Wz = (const WT *)a.W + (size_t)z * a.rs;
@@ -203,7 +209,7 @@ __global__ void __launch_bounds__(TK * 32) dmc_wcols_kernel(const GemvArgs a) {
     bool cok[V];
 #pragma unroll
     for (int v = 0; v < V; ++v) {
-        col[v] = cb * CW + (v * 32 + lane) * EPV;
+        col[v] = cb * CW + (v * LPR + lcol) * EPV;
         cok[v] = col[v] < N;
     }
 
@@ -219,7 +225,7 @@ __global__ void __launch_bounds__(TK * 32) dmc_wcols_kernel(const GemvArgs a) {
     auto load_w = [&](int k) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int kk = k + u * TK;
+            const int kk = k + u * TK * NR;
 #pragma unroll
             for (int v = 0; v < V; ++v)
                 w[u][v] = (kk < kend && cok[v]) ? ldg_stream16(Wz + (size_t)kk * N + col[v])
@@ -230,7 +236,7 @@ __global__ void __launch_bounds__(TK * 32) dmc_wcols_kernel(const GemvArgs a) {
         float xv[M][U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int kk = k + u * TK;
+            const int kk = k + u * TK * NR;
 #pragma unroll
             for (int m = 0; m < M; ++m) xv[m][u] = kk < kend ? __ldcg(xz + (size_t)m * K + kk) : 0.0f;
         }
@@ -242,17 +248,30 @@ __global__ void __launch_bounds__(TK * 32) dmc_wcols_kernel(const GemvArgs a) {
                 for (int v = 0; v < V; ++v) axpy_vec<WT>(acc[m][v], w[u][v], xv[m][u]);
     };
 
-    int k = kbeg + warp;
+    int k = kbeg + warp * NR + sub;
     if (k < kend) load_w(k);
     griddep_launch_dependents();
     griddep_wait();
     if (k < kend) {
         consume(k);
-        k += TK * U;
+        k += TK * U * NR;
     }
-    for (; k < kend; k += TK * U) {
+    for (; k < kend; k += TK * U * NR) {
         load_w(k);
         consume(k);
+    }
+    if constexpr (NR > 1) {  // the NR partial rows of a warp meet in its first LPR lanes
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+            for (int v = 0; v < V; ++v)
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) {
+                    float s = acc[m][v][e];
+                    s += __shfl_xor_sync(0xffffffffu, s, 16);
+                    if constexpr (NR == 4) s += __shfl_xor_sync(0xffffffffu, s, 8);
+                    acc[m][v][e] = s;
+                }
     }
 
     // warps -> CTA, one x row at a time (keeps shared memory at TK*CW floats)
@@ -261,10 +280,12 @@ __global__ void __launch_bounds__(TK * 32) dmc_wcols_kernel(const GemvArgs a) {
         if (m) __syncthreads();
 #pragma unroll
         for (int v = 0; v < V; ++v) {
-            float4 *dst = reinterpret_cast<float4 *>(&red[warp][(v * 32 + lane) * EPV]);
-            dst[0] = make_float4(acc[m][v][0], acc[m][v][1], acc[m][v][2], acc[m][v][3]);
-            if constexpr (EPV == 8)
-                dst[1] = make_float4(acc[m][v][4], acc[m][v][5], acc[m][v][6], acc[m][v][7]);
+            if (sub == 0) {
+                float4 *dst = reinterpret_cast<float4 *>(&red[warp][(v * LPR + lcol) * EPV]);
+                dst[0] = make_float4(acc[m][v][0], acc[m][v][1], acc[m][v][2], acc[m][v][3]);
+                if constexpr (EPV == 8)
+                    dst[1] = make_float4(acc[m][v][4], acc[m][v][5], acc[m][v][6], acc[m][v][7]);
+            }
         }
         __syncthreads();
         for (int c = threadIdx.x; c < CW; c += THREADS) {
@@ -330,7 +351,7 @@ __global__ void __launch_bounds__(TK * 32) dmc_wcols_any_kernel(const GemvArgs a
 // is either one group per warp (when that fits in one wave) or exactly
 // SMs x resident CTAs, every CTA with the same share of the rows.
 // Needs K % EPV == 0 and a 16-byte aligned W.  Dynamic shared memory: M rows of
-// K floats, each rounded up to a multiple of 256 floats.
+// K floats, each rounded up to a multiple of 256 floats plus 256 zeros.
 // STAMP = true is the same kernel with five time stamps per CTA (GemvArgs::stamps), used only by the
 // time-line measurement; the product instantiations carry none of it.
 template <int WARPS, int R, int U, int M, typename WT, bool STAMP = false>
@@ -344,7 +365,8 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int K = a.K, N = a.N;
     const int nvec = K / EPV;
-    const int xrow4 = (K + 255) / 256 * 64;  // float4 slots per staged row of x
+    const int xpad4 = (K + 255) / 256 * 64;  // float4 slots of one staged row of x ...
+    const int xrow4 = xpad4 + 64;            // ... followed by a block of zeros
     const uint4 *W4 = reinterpret_cast<const uint4 *>(a.W);
 
     // this CTA's block of row groups
@@ -369,19 +391,14 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
     auto consume = [&](int c) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
+            // vectors past the end of a row (loaded as zeros) read a block of zeros kept behind the staged row,
+            // instead of predicating every shared-memory read
             const int cc = c + 32 * u;
+            // per 32 vectors: low halves first, then high halves
+            const int xi = cc < nvec ? (EPV == 8 ? (cc >> 5) * 64 + (cc & 31) : cc) : xpad4;
             if constexpr (M == 1) {
-                float4 xa = make_float4(0, 0, 0, 0), xb = xa;
-                if (cc < nvec) {
-                    if constexpr (EPV == 8) {
-                        // block of 32 vectors = 64 float4: low halves first, then high halves
-                        const int blk = cc >> 5, l = cc & 31;
-                        xa = xs4[blk * 64 + l];
-                        xb = xs4[blk * 64 + 32 + l];
-                    } else {
-                        xa = xs4[cc];
-                    }
-                }
+                const float4 xa = xs4[xi];
+                const float4 xb = EPV == 8 ? xs4[xi + 32] : make_float4(0, 0, 0, 0);
 #pragma unroll
                 for (int j = 0; j < R; ++j) acc[j][0][u & 1] = dot_vec<WT>(acc[j][0][u & 1], w[j][u], xa, xb);
             } else {
@@ -391,16 +408,8 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
                 for (int j = 0; j < R; ++j) widen_vec<WT>(w[j][u], wf[j]);
 #pragma unroll
                 for (int m = 0; m < M; ++m) {
-                    float4 xa = make_float4(0, 0, 0, 0), xb = xa;
-                    if (cc < nvec) {
-                        if constexpr (EPV == 8) {
-                            const int blk = cc >> 5, l = cc & 31;
-                            xa = xs4[m * xrow4 + blk * 64 + l];
-                            xb = xs4[m * xrow4 + blk * 64 + 32 + l];
-                        } else {
-                            xa = xs4[m * xrow4 + cc];
-                        }
-                    }
+                    const float4 xa = xs4[m * xrow4 + xi];
+                    const float4 xb = EPV == 8 ? xs4[m * xrow4 + xi + 32] : make_float4(0, 0, 0, 0);
 #pragma unroll
                     for (int j = 0; j < R; ++j) {
                         float s = acc[j][m][0];
@@ -454,22 +463,57 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
             }
         };
         const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
+        for (int i = threadIdx.x; i < 64 * M; i += THREADS) xs4[(i >> 6) * xrow4 + xpad4 + (i & 63)] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (M == 1 && a.pro == 1) {
             // RMSNorm of the residual stream fused into the staging (f32 form of the JIT,
             // compiler/src/jit.rs:23776-23847): every CTA normalises its own copy of x
+            // Loads are issued in batches (x, the residual and the gain of up to PG elements per thread
+            // before anything is used): the staging sits on the critical path of a dependent chain, and
+            // every separate round trip to L2 costs ~0.3 us there.
             __shared__ float red[WARPS];
+            constexpr int PG = 4;
             const float4 *add4 = reinterpret_cast<const float4 *>(a.pro_add);
+            const float4 *g4 = reinterpret_cast<const float4 *>(a.pro_g);
             float4 *h4 = reinterpret_cast<float4 *>(a.pro_hout);
+            float4 v[PG], gg[PG];
             float ss = 0.0f;
-            for (int i = threadIdx.x; i < n4; i += THREADS) {
-                float4 v = __ldcg(x4 + i);
+#pragma unroll
+            for (int j = 0; j < PG; ++j) {
+                const int i = threadIdx.x + j * THREADS;
+                v[j] = i < n4 ? __ldcg(x4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            if (add4) {
+#pragma unroll
+                for (int j = 0; j < PG; ++j) {
+                    const int i = threadIdx.x + j * THREADS;
+                    if (i < n4) {
+                        const float4 d = __ldcg(add4 + i);
+                        v[j].x += d.x, v[j].y += d.y, v[j].z += d.z, v[j].w += d.w;
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < PG; ++j) {
+                const int i = threadIdx.x + j * THREADS;
+                gg[j] = i < n4 ? __ldg(g4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < PG; ++j) {
+                const int i = threadIdx.x + j * THREADS;
+                if (i < n4) {
+                    if (h4 && blockIdx.x == 0) h4[i] = v[j];
+                    ss = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, ss))));
+                }
+            }
+            for (int i = threadIdx.x + PG * THREADS; i < n4; i += THREADS) {  // rows longer than PG * THREADS vectors
+                float4 t = __ldcg(x4 + i);
                 if (add4) {
                     const float4 d = __ldcg(add4 + i);
-                    v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
+                    t.x += d.x, t.y += d.y, t.z += d.z, t.w += d.w;
                 }
-                if (h4 && blockIdx.x == 0) h4[i] = v;
-                ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
-                slot(0, i) = v;
+                if (h4 && blockIdx.x == 0) h4[i] = t;
+                ss = fmaf(t.x, t.x, fmaf(t.y, t.y, fmaf(t.z, t.z, fmaf(t.w, t.w, ss))));
+                slot(0, i) = t;
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -479,23 +523,43 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
 #pragma unroll
             for (int w2 = 0; w2 < WARPS; ++w2) tot += red[w2];
             const float inv = 1.0f / sqrtf(tot / (float)K + a.pro_eps);
-            const float4 *g4 = reinterpret_cast<const float4 *>(a.pro_g);
-            for (int i = threadIdx.x; i < n4; i += THREADS) {  // each thread rescales what it stored itself
-                float4 v = slot(0, i);
-                const float4 gg = __ldg(g4 + i);
-                v.x = v.x * gg.x * inv, v.y = v.y * gg.y * inv, v.z = v.z * gg.z * inv, v.w = v.w * gg.w * inv;
-                slot(0, i) = v;
+#pragma unroll
+            for (int j = 0; j < PG; ++j) {  // the first PG elements per thread never left the registers
+                const int i = threadIdx.x + j * THREADS;
+                if (i < n4) {
+                    float4 t = v[j];
+                    t.x = t.x * gg[j].x * inv, t.y = t.y * gg[j].y * inv, t.z = t.z * gg[j].z * inv, t.w = t.w * gg[j].w * inv;
+                    slot(0, i) = t;
+                }
+            }
+            for (int i = threadIdx.x + PG * THREADS; i < n4; i += THREADS) {  // each thread rescales what it stored itself
+                float4 t = slot(0, i);
+                const float4 g1 = __ldg(g4 + i);
+                t.x = t.x * g1.x * inv, t.y = t.y * g1.y * inv, t.z = t.z * g1.z * inv, t.w = t.w * g1.w * inv;
+                slot(0, i) = t;
             }
         } else if (M == 1 && a.pro == 2) {
             // SwiGLU (silu = x / (1 + e^-x), compiler/src/interp.rs:13418) of a [gate | up] vector
-            for (int i = threadIdx.x; i < n4; i += THREADS) {
-                const float4 gt = __ldcg(x4 + i), up = __ldcg(x4 + n4 + i);
-                float4 v;
-                v.x = gt.x / (1.0f + __expf(-gt.x)) * up.x;
-                v.y = gt.y / (1.0f + __expf(-gt.y)) * up.y;
-                v.z = gt.z / (1.0f + __expf(-gt.z)) * up.z;
-                v.w = gt.w / (1.0f + __expf(-gt.w)) * up.w;
-                slot(0, i) = v;
+            constexpr int PG = 4;
+            for (int i0 = threadIdx.x; i0 < n4; i0 += PG * THREADS) {
+                float4 gt[PG], up[PG];
+#pragma unroll
+                for (int j = 0; j < PG; ++j) {
+                    const int i = i0 + j * THREADS;
+                    if (i < n4) gt[j] = __ldcg(x4 + i), up[j] = __ldcg(x4 + n4 + i);
+                }
+#pragma unroll
+                for (int j = 0; j < PG; ++j) {
+                    const int i = i0 + j * THREADS;
+                    if (i < n4) {
+                        float4 v;
+                        v.x = gt[j].x / (1.0f + __expf(-gt[j].x)) * up[j].x;
+                        v.y = gt[j].y / (1.0f + __expf(-gt[j].y)) * up[j].y;
+                        v.z = gt[j].z / (1.0f + __expf(-gt[j].z)) * up[j].z;
+                        v.w = gt[j].w / (1.0f + __expf(-gt[j].w)) * up[j].w;
+                        slot(0, i) = v;
+                    }
+                }
             }
         } else {
 #pragma unroll

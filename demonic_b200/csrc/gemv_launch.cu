@@ -1,6 +1,7 @@
 // gemv_launch.cu -- kernel-configuration tables and launch planning for the GEMV kernels.
 #include <algorithm>
 #include <cstdio>
+#include <map>
 #include <set>
 
 #include "gemv.cuh"
@@ -49,6 +50,17 @@ static const KnVariant kKn[] = {
 };
 constexpr int kKnCount = sizeof(kKn) / sizeof(kKn[0]);
 
+// Narrow matrices (n <= 128: the per-head projections of the batched entry points): 2 or 4 k rows per
+// warp-wide load, so that every lane carries a vector.
+struct KnNarrow {
+    int max_n, NR, TK, U;
+    KernelFn bf16, f32;
+};
+static const KnNarrow kKnNarrow[] = {
+    {64, 4, 8, 8, dmc_wcols_kernel<8, 8, 1, 1, uint16_t, 4>, dmc_wcols_kernel<8, 8, 1, 1, float, 2>},   // f32: 4 columns per vector
+    {128, 2, 8, 8, dmc_wcols_kernel<8, 8, 1, 1, uint16_t, 2>, dmc_wcols_kernel<8, 8, 1, 1, float, 1>},
+};
+
 struct NkVariant {
     const char *name;
     int WARPS, R, U;
@@ -75,8 +87,8 @@ struct NkRows {
 };
 static const NkRows kNkRows[] = {
     {2, 8, 2, 8, dmc_wrows_kernel<8, 2, 8, 2, uint16_t>, dmc_wrows_kernel<8, 2, 8, 2, float>},
-    {4, 8, 4, 4, dmc_wrows_kernel<8, 4, 4, 4, uint16_t>, dmc_wrows_kernel<8, 4, 4, 4, float>},
-    {8, 8, 4, 4, dmc_wrows_kernel<8, 4, 4, 8, uint16_t>, dmc_wrows_kernel<8, 4, 4, 8, float>},
+    {4, 8, 2, 4, dmc_wrows_kernel<8, 2, 4, 4, uint16_t>, dmc_wrows_kernel<8, 2, 4, 4, float>},
+    {8, 16, 4, 2, dmc_wrows_kernel<16, 4, 2, 8, uint16_t>, dmc_wrows_kernel<16, 4, 2, 8, float>},
 };
 
 // ---- which launches may overlap -----------------------------------------------------------
@@ -167,14 +179,16 @@ namespace {
 // Default configuration per shape (from sweeps on B200 over every configuration in the tables above).
 int default_kn_variant(int64_t k, int64_t n) {
     (void)k;
-    (void)n;
-    return 3;
+    return n <= 256 ? 1 : 3;  // one vector per lane when a row has no more than 32 of them; else two
 }
 int default_nk_variant(int64_t k, int64_t n) {
     // B200 sweeps: 8 warps x 2 rows x 8 loads in flight is within ~2 % of the best configuration on
-    // every decode shape; long rows of a big matrix do a little better with 4 rows x 4 loads.
-    if (k >= 8192 && n >= 8192) return 1;  // nk_w8_r4_u4
-    return 0;                              // nk_w8_r2_u8
+    // every decode shape; long rows of a big matrix do a little better with 4 rows x 4 loads.  A
+    // matrix with so few rows that two rows per warp would leave SMs without a CTA (a 2048-row
+    // output projection: 128 CTAs on 148 SMs) takes one row per warp instead.
+    if (k >= 8192 && n >= 8192) return 1;                 // nk_w8_r4_u4
+    if ((n + 15) / 16 < ctx().sm_count) return 3;         // nk_w8_r1_u8
+    return 0;                                             // nk_w8_r2_u8
 }
 
 int launch_kn(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
@@ -200,26 +214,38 @@ int launch_kn(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
                                               : (const void *)dmc_wcols_any_kernel<8, float>;
         return launch_ex(fn, dim3((unsigned)(a.colblocks * batch)), dim3(256), 0, stream, params);
     }
+    // narrow matrices: the form in which every lane loads (bf16 n <= 128, f32 n <= 64)
+    const KnNarrow *narrow = nullptr;
+    if (variant < 0 && m == 1)
+        for (const KnNarrow &c2 : kKnNarrow)
+            if (!narrow && n * (wdtype == DMC_W_BF16 ? 1 : 2) <= c2.max_n) narrow = &c2;
     if (variant < 0 || variant >= kKnCount) variant = default_kn_variant(k, n);
     // rows of x beyond what one kernel instance holds are processed in chunks
     for (int64_t m0 = 0; m0 < m;) {
         const int64_t left = m - m0;
         int mi = left >= 8 ? 3 : left >= 4 ? 2 : left >= 2 ? 1 : 0;
         const int M = 1 << mi;
-        const KnVariant &v = (M == 1) ? kKn[variant] : kKn[0];
+        KnVariant v = (M == 1) ? kKn[variant] : kKn[0];
         KernelFn fn = wdtype == DMC_W_BF16 ? v.bf16[mi] : v.f32[mi];
-        const int cw = 32 * v.V * epv;
+        int nr = 1;
+        if (narrow) {
+            nr = wdtype == DMC_W_BF16 ? narrow->NR : narrow->NR / 2;
+            fn = wdtype == DMC_W_BF16 ? narrow->bf16 : narrow->f32;
+            v.TK = narrow->TK, v.U = narrow->U, v.V = 1, v.ctas_per_sm = 4;
+        }
+        const int cw = (32 / nr) * v.V * epv;
         a.colblocks = (int)((n + cw - 1) / cw);
         const int64_t base_ctas = (int64_t)a.colblocks * batch;
         const int cps = tuning().kn_ctas_per_sm > 0 ? tuning().kn_ctas_per_sm : v.ctas_per_sm;
         int64_t ksplit = tuning().kn_ksplit > 0 ? tuning().kn_ksplit
                                                  : ((int64_t)c.sm_count * cps + base_ctas / 2) / base_ctas;
-        const int64_t step = (int64_t)v.TK * v.U;
+        const int64_t step = (int64_t)v.TK * v.U * nr;
         ksplit = std::max<int64_t>(1, std::min<int64_t>(ksplit, (k + step - 1) / step));
         ksplit = std::min<int64_t>(ksplit, 65535);
         int64_t kchunk = (k + ksplit - 1) / ksplit;
-        kchunk = (kchunk + v.TK - 1) / v.TK * v.TK;
-        if (kchunk < 1) kchunk = v.TK;
+        const int64_t kq = (int64_t)v.TK * nr;
+        kchunk = (kchunk + kq - 1) / kq * kq;
+        if (kchunk < 1) kchunk = kq;
         ksplit = std::max<int64_t>(1, (k + kchunk - 1) / kchunk);
         a.kchunk = (int)kchunk;
         a.ksplit = (int)ksplit;
@@ -345,7 +371,7 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
               int wdtype, int variant, cudaStream_t stream) {
     Context &c = ctx();
     const int epv = wdtype == DMC_W_BF16 ? 8 : 4;
-    const size_t xrow = (size_t)((k + 255) / 256 * 256) * sizeof(float);  // one staged row of x
+    const size_t xrow = (size_t)((k + 255) / 256 * 256 + 256) * sizeof(float);  // one staged row of x
     const bool vec_ok = k % epv == 0 && ((uintptr_t)dW % 16) == 0 && ((uintptr_t)dx % 16) == 0 &&
                         xrow <= kNkMaxSmem;
     if (c.pro) {
@@ -410,10 +436,17 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
             DMC_CUDA_TRY(cudaFuncSetAttribute((const void *)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNkMaxSmem));
             smem_raised.insert((const void *)fn);
         }
-        const int by_threads = 2048 / (warps * 32);
-        const int by_smem = (int)std::max<size_t>(1, (220 * 1024) / (smem + 1024));
-        int cps = std::min(2, std::min(by_threads, by_smem));  // the kernels use ~100-128 registers: two CTAs of 8 warps
-        if (tuning().nk_ctas_per_sm > 0) cps = std::min(std::min(by_threads, by_smem), tuning().nk_ctas_per_sm);
+        // resident CTAs per SM of this instance with this much shared memory (registers decide: 1 or 2)
+        static std::map<std::pair<const void *, size_t>, int> occupancy;
+        auto key = std::make_pair((const void *)fn, smem);
+        auto it = occupancy.find(key);
+        if (it == occupancy.end()) {
+            int blocks = 1;
+            DMC_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, (const void *)fn, warps * 32, smem));
+            it = occupancy.emplace(key, std::max(1, blocks)).first;
+        }
+        int cps = it->second;
+        if (tuning().nk_ctas_per_sm > 0) cps = std::min(cps, tuning().nk_ctas_per_sm);
         const int64_t grid = nk_grid(n, warps, r, c.sm_count, cps);
         a.x = dx + m0 * k;
         a.y = dy + m0 * n;
@@ -448,7 +481,7 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
 int timeline_nk(const void *const *dWs, int count, const float *dx, float *dy, int64_t k, int64_t n, int dependent,
                 unsigned long long *stamps_out, int64_t stamps_cap_words, cudaStream_t s) {
     Context &c = ctx();
-    const size_t xrow = (size_t)((k + 255) / 256 * 256) * sizeof(float);
+    const size_t xrow = (size_t)((k + 255) / 256 * 256 + 256) * sizeof(float);
     if (k % 8 || xrow > kNkMaxSmem || count < 1)
         return -fail(DMC_CUDA_ERR_UNSUPPORTED, "timeline: needs k %% 8 == 0, a row of x that fits shared memory, count >= 1");
     const void *fn = (const void *)dmc_wrows_kernel<8, 2, 8, 1, uint16_t, true>;
@@ -488,7 +521,7 @@ int timeline_nk(const void *const *dWs, int count, const float *dx, float *dy, i
 
 bool nk_fast_eligible(int64_t k, int64_t n, int wdtype) {
     const int epv = wdtype == DMC_W_BF16 ? 8 : 4;
-    return n >= 1 && k >= 512 && k % epv == 0 && (size_t)((k + 255) / 256 * 256) * sizeof(float) <= kNkMaxSmem;
+    return n >= 1 && k >= 512 && k % epv == 0 && (size_t)((k + 255) / 256 * 256 + 256) * sizeof(float) <= kNkMaxSmem;
 }
 
 int launch_transpose(const void *src, void *dst, int64_t rows, int64_t cols, int elem_bytes, cudaStream_t stream) {

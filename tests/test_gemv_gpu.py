@@ -184,6 +184,31 @@ def test_batched_strides(batch, ls_full, rs_full):
         assert_parity(out[z], ref[z], 1e-5, f"slice {z}")
 
 
+@pytest.mark.parametrize("n", [8, 32, 64, 72, 128, 136])
+@pytest.mark.parametrize("k", [128, 1000, 2560])
+def test_narrow_per_head_projections(n, k):
+    """Narrow matrices (the per-head projections: n = 128 or 64) run in the form where a warp-wide load
+    covers 2 or 4 k rows; widths around the switch points, k not a multiple of the row tiling, several
+    split-K factors, bf16 and f32."""
+    lib = dmc.load()
+    batch = 5
+    rng = np.random.default_rng(1000 * n + k)
+    x = synth.activations(rng, (1, k))
+    w = synth.bf16_weights(rng, (batch, k, n))
+    ref = np.stack([oracle.gemm_bf16_fma(x, w[z])[0] for z in range(batch)])
+    for ksplit in (0, 1, 3):
+        lib.dmc_cuda_set_param(b"kn_ksplit", ksplit)
+        out = np.full((batch, n), np.nan, F)
+        dmc.matmul_bf16_gpu_batched(x, w, out, 1, k, n, batch, 0, k * n)
+        for z in range(batch):
+            assert_parity(out[z], ref[z], TOL_BF16, f"bf16 n={n} k={k} ksplit={ksplit} slice {z}")
+    lib.dmc_cuda_set_param(b"kn_ksplit", 0)
+    wf = synth.f32_weights(rng, (k, n), std=1.0)
+    out = np.full((1, n), np.nan, F)
+    dmc.matmul_f32_gpu(x, wf, out, 1, k, n)
+    assert_parity(out, oracle.gemm_f32_fma(x, wf), TOL_F32, f"f32 n={n} k={k}")
+
+
 def test_batched_unaligned_stride_uses_generic_kernel():
     k, n, batch = 33, 12, 3          # rs = 396, not a multiple of 8
     rng = np.random.default_rng(77)
