@@ -74,6 +74,10 @@ static FpKey fingerprint(const uint8_t *ptr, size_t bytes) {
     if (words > 0) {
         size_t step = words / 256;
         if (step < 1) step = 1;
+        // the samples are ~256 cache lines spread over the whole weight: ask for all of them first, so the
+        // misses overlap instead of queueing behind the hash chain
+        if (step >= 8)
+            for (size_t i = 0; i < words; i += step) __builtin_prefetch(ptr + 8 * i, 0, 0);
         for (size_t i = 0; i < words; i += step) {
             uint64_t v;
             memcpy(&v, ptr + 8 * i, 8);

@@ -35,6 +35,7 @@ struct GemvArgs {
     // running, so the programmatic-dependency wait is skipped and the launch overlaps its
     // predecessors freely (set by the launch planner, never by a caller)
     int nowait;
+    int mrows;           // NK kernel with M > 1: rows of x actually present (1..M); the others are staged as zeros
     const PeerOut *peer; // NK kernel, sharded path: store y into every rank's replica (else null)
     long long yoff;      // first row of this rank's slice within the replicated y
     int peer_j;          // position of this exchange in the current batch of launches
@@ -564,7 +565,8 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
         } else {
 #pragma unroll
             for (int m = 0; m < M; ++m)
-                for (int i = threadIdx.x; i < n4; i += THREADS) slot(m, i) = __ldcg(x4 + (size_t)m * n4 + i);
+                for (int i = threadIdx.x; i < n4; i += THREADS)
+                    slot(m, i) = (M == 1 || m < a.mrows) ? __ldcg(x4 + (size_t)m * n4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         __syncthreads();
     }
@@ -597,7 +599,7 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
                 const int row = row0 + j;
                 if (M == 1 && peer) {
                     if (lane == j) mine = s;
-                } else if (lane == 0 && row < N) {
+                } else if (lane == 0 && row < N && (M == 1 || m < a.mrows)) {
                     a.y[(size_t)m * N + row] = s;
                 }
                 if (M == 1 && a.amax && row < N && s == s) {  // (a NaN is never a maximum)

@@ -333,11 +333,11 @@ def test_registered_matrix_is_stored_k_contiguous():
     lib.dmc_cuda_drop_resident()
 
 
-@pytest.mark.parametrize("m", [2, 3, 4, 5, 8, 9, 16])
+@pytest.mark.parametrize("m", [2, 3, 4, 5, 7, 8, 9, 16])
 def test_small_batch_keeps_f32_rows_on_the_cuda_cores(m):
     """x @ w' with a few f32 rows of x on a k-contiguous weight: up to 8 rows share every weight load
     in the multi-row kernel with exact f32 activations (parity at the f32-order level, far inside 1e-2);
-    more rows go to the tensor cores."""
+    more rows go to the tensor cores.  With `tc_min_m` raised, 9 and 16 rows stay on the CUDA cores too."""
     k, n = 4096, 4096
     rng = np.random.default_rng(700 + m)
     w = synth.bf16_weights(rng, (n, k))
@@ -352,7 +352,16 @@ def test_small_batch_keeps_f32_rows_on_the_cuda_cores(m):
     err = assert_parity(out, ref, TOL_BF16, f"m={m}")
     if m <= 8:
         assert err < 1e-5, f"m={m}: the CUDA-core rows use exact f32 activations (got {err:.2e})"
-        assert launches == bin(m).count("1"), "rows taken 8, 4, 2 or 1 at a time, W streamed once per instance"
+        assert launches == 1, "up to 8 rows in one instance: W streamed once"
+    lib.dmc_cuda_set_param(b"tc_min_m", 1 << 20)                # every row count on the CUDA cores
+    try:
+        out2 = np.full((m, n), np.nan, F)
+        before = lib.dmc_cuda_launch_count()
+        dmc.matmul_bf16_gpu_nt(x, w, out2, m, k, n)
+        assert lib.dmc_cuda_launch_count() - before == -(-m // 8)
+        assert assert_parity(out2, ref, TOL_BF16, f"m={m} cuda cores") < 1e-5
+    finally:
+        lib.dmc_cuda_set_param(b"tc_min_m", 0)
 
 
 def test_batched_slices_with_several_rows_run_on_the_gpu():
