@@ -88,7 +88,7 @@ struct NkRows {
 };
 static const NkRows kNkRows[] = {
     {2, 8, 2, 8, dmc_wrows_kernel<8, 2, 8, 2, uint16_t>, dmc_wrows_kernel<8, 2, 8, 2, float>},
-    {4, 8, 2, 4, dmc_wrows_kernel<8, 2, 4, 4, uint16_t>, dmc_wrows_kernel<8, 2, 4, 4, float>},
+    {4, 8, 2, 8, dmc_wrows_kernel<8, 2, 8, 4, uint16_t>, dmc_wrows_kernel<8, 2, 8, 4, float>},
     {8, 16, 4, 2, dmc_wrows_kernel<16, 4, 2, 8, uint16_t>, dmc_wrows_kernel<16, 4, 2, 8, float>},
 };
 
@@ -183,11 +183,12 @@ int default_kn_variant(int64_t k, int64_t n) {
     return n <= 256 ? 1 : 3;  // one vector per lane when a row has no more than 32 of them; else two
 }
 int default_nk_variant(int64_t k, int64_t n) {
-    // B200 sweeps: 8 warps x 2 rows x 8 loads in flight is within ~2 % of the best configuration on
-    // every decode shape; long rows of a big matrix do a little better with 4 rows x 4 loads.  A
-    // matrix with so few rows that two rows per warp would leave SMs without a CTA (a 2048-row
-    // output projection: 128 CTAs on 148 SMs) takes one row per warp instead.
-    if (k >= 8192 && n >= 8192) return 1;                 // nk_w8_r4_u4
+    // B200 sweeps: 8 warps x 2 rows x 8 loads in flight is the best or within 1 % of the best
+    // configuration on every shape from 4096x4096 to 65536x8192 (4 rows x 4 loads: 22.0 vs 21.7 us at
+    // 8192x8192 in a dependent chain, 81.0 vs 79.6 at 32768x8192).  A matrix with so few rows that two
+    // rows per warp would leave SMs without a CTA (a 2048-row output projection: 128 CTAs on 148 SMs)
+    // takes one row per warp instead.
+    (void)k;
     if ((n + 15) / 16 < ctx().sm_count) return 3;         // nk_w8_r1_u8
     return 0;                                             // nk_w8_r2_u8
 }
@@ -365,6 +366,8 @@ int64_t nk_grid(int64_t n, int warps, int r, int sm_count, int cps) {
     const int64_t groups = (n + r - 1) / r;
     const int64_t exact = (groups + warps - 1) / warps;
     const int64_t slots = (int64_t)sm_count * cps;
+    // (when the groups do not even fill one CTA per SM, one group per warp still wins: measured at
+    // 4096x4096 with 8 rows of x, 64 full CTAs 10.8 us against 148 CTAs with idle warps 17.0 us)
     return std::max<int64_t>(1, exact <= slots ? exact : slots);
 }
 
