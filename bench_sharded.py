@@ -74,7 +74,9 @@ def run(args, rank: int, world: int) -> None:
     sharded.init(rank, world, ids[0], ROWS)
     r0, r1 = sharded.shard_range(ROWS, rank, world)
     w = shard_weights(r0, r1, seed)
-    copies = max(1, -(-ROTATE_BYTES // w.nbytes)) if w.nbytes < ROTATE_BYTES else 1
+    # at least four GEMVs per step (a batch of independent exchanges: adjacent ones overlap), over distinct
+    # copies of the shard that together exceed L2 several times
+    copies = max(4, -(-ROTATE_BYTES // w.nbytes))
     bufs = [backend.DeviceBuffer.from_host(w) for _ in range(copies)]
     y_ref = oracle_full_y(rank, world, w, x, r0, r1, dist)
 
@@ -115,8 +117,10 @@ def run(args, rank: int, world: int) -> None:
     dist.barrier()
     # the same step with each exchange forced: fused into the kernel (peer stores) and ncclAllGather
     forced, per_exchange = {}, {}
-    for name, mode in (("fused_peer_stores", 1), ("nccl_allgather", 0)):
+    for name, mode, overlap in (("fused_peer_stores", 1, 1), ("fused_peer_stores_one_exchange_at_a_time", 1, 0),
+                                ("nccl_allgather", 0, 1)):
         lib.dmc_cuda_set_param(b"shard_fused", mode)
+        lib.dmc_cuda_set_param(b"shard_overlap", overlap)
         dist.barrier()
         u = sharded.bench(bufs, dx, COLS, ROWS, args.steps, args.warmup, use_graph=True)
         backend.sync()
@@ -125,6 +129,7 @@ def run(args, rank: int, world: int) -> None:
         forced[name] = max(v[0] for v in allu) / copies
         per_exchange[name] = check(f"after the run with {name}")
     lib.dmc_cuda_set_param(b"shard_fused", -1)
+    lib.dmc_cuda_set_param(b"shard_overlap", 1)
     parity["per_exchange"] = per_exchange
     parity["scaled_err_max_over_ranks"] = max([parity["before_timing"], parity["after_timed_region"], *per_exchange.values()])
     alg = synth.gemv_bytes(ROWS, COLS)            # whole job: every weight byte once + x + y

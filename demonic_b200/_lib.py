@@ -47,6 +47,7 @@ SIGNATURES = {
     "dmc_cuda_shard_init": (C.c_int, [C.c_int, C.c_int, VP, I64]),
     "dmc_cuda_shard_shutdown": (None, []),
     "dmc_cuda_shard_gemv": (C.c_int, [VP, VP, I64, I64, C.c_int]),
+    "dmc_cuda_shard_gemv_batch": (C.c_int, [VP, C.c_int, VP, VP, I64, I64, C.c_int]),
     "dmc_cuda_shard_output": (VP, []),
     "dmc_cuda_shard_output_previous": (VP, []),
     "dmc_cuda_shard_uses_fused": (C.c_int, [I64, I64]),

@@ -641,6 +641,7 @@ static int apply_param(const char *name, int64_t value) {
     else if (!strcmp(name, "store_nk")) t.store_nk = (int)value;
     else if (!strcmp(name, "nk_default")) t.nk_default = (int)value;
     else if (!strcmp(name, "shard_fused")) t.shard_fused = (int)value;
+    else if (!strcmp(name, "shard_overlap")) t.shard_overlap = (int)value;
     else if (!strcmp(name, "overlap_independent")) t.overlap_independent = (int)value;
     else if (!strcmp(name, "wait_limit_us")) t.wait_limit_us = (int)value;
     else if (!strcmp(name, "timing")) t.timing = (int)value;

@@ -433,7 +433,10 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
 
     unsigned long long t_entry = 0, t_wait = 0, t_x = 0, t_first = 0;
     if (STAMP && threadIdx.x == 0) t_entry = globaltimer_ns();
-    griddep_launch_dependents();
+    // (the first exchange of a batch lets its dependents go only after its own wait: they read the
+    // epoch word that the end of the previous batch advances)
+    const bool hold_dependents = a.peer != nullptr && a.peer_j == 0;
+    if (!hold_dependents) griddep_launch_dependents();
     int g = g0 + warp;
     if (g < g1) load_w(g * R, lane);  // weights depend on no earlier kernel: first loads go out before the wait
     // The exchange descriptor is copied into shared memory once per CTA: read through the global
@@ -446,11 +449,17 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
             reinterpret_cast<unsigned *>(&s_peer)[i] = __ldg(reinterpret_cast<const unsigned *>(a.peer) + i);
     }
     if (!a.nowait) griddep_wait();
+    if (hold_dependents) griddep_launch_dependents();
     if (STAMP && threadIdx.x == 0) t_wait = globaltimer_ns();
     // after the wait: an earlier kernel (the end of the previous batch) is what advances the epoch word
     const PeerOut *peer = a.peer ? &s_peer : nullptr;
     if (a.peer) __syncthreads();  // the descriptor copy is complete
     const unsigned epoch = peer ? peer_epoch(peer, a.peer_j) : 0u;
+    // the replica buffer of this exchange must be free again: the words that say so are requested here
+    // and looked at once x is staged; the barrier there orders every warp's stores after the check
+    __shared__ __align__(16) unsigned guard_words[kMaxPeers];
+    const bool guard = peer != nullptr && threadIdx.x == 0 && epoch >= 3u;
+    if (guard) peer_guard_load(peer, guard_words);
 
     // stage x (after the dependency wait: an earlier kernel may produce it)
     {
@@ -568,6 +577,7 @@ __global__ void __launch_bounds__(WARPS * 32) dmc_wrows_kernel(const GemvArgs a)
                 for (int i = threadIdx.x; i < n4; i += THREADS)
                     slot(m, i) = (M == 1 || m < a.mrows) ? __ldcg(x4 + (size_t)m * n4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
+        if (guard && !peer_guard_ok(peer, epoch, guard_words)) peer_wait_buffer_free(peer, epoch);
         __syncthreads();
     }
     if (STAMP && threadIdx.x == 0) t_x = globaltimer_ns();

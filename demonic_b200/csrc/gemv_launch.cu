@@ -362,10 +362,10 @@ int launch_nk_tma(const TmaPlan &p, const void *dW, const float *dx, float *dy, 
 // Grid of the NK kernel: one row group per warp when the whole matrix then fits in one wave of
 // resident CTAs (no warp idles, no CTA loops); otherwise exactly SMs x resident CTAs, every CTA
 // owning the same share of the row groups (the kernel splits them evenly by block index).
-int64_t nk_grid(int64_t n, int warps, int r, int sm_count, int cps) {
+int64_t nk_grid(int64_t n, int warps, int r, int sm_count, int cps, int reserve = 0) {
     const int64_t groups = (n + r - 1) / r;
     const int64_t exact = (groups + warps - 1) / warps;
-    const int64_t slots = (int64_t)sm_count * cps;
+    const int64_t slots = std::max<int64_t>(1, (int64_t)sm_count * cps - reserve);
     // (when the groups do not even fill one CTA per SM, one group per warp still wins: measured at
     // 4096x4096 with 8 rows of x, 64 full CTAs 10.8 us against 148 CTAs with idle warps 17.0 us)
     return std::max<int64_t>(1, exact <= slots ? exact : slots);
@@ -453,14 +453,17 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
         }
         int cps = it->second;
         if (tuning().nk_ctas_per_sm > 0) cps = std::min(cps, tuning().nk_ctas_per_sm);
-        const int64_t grid = nk_grid(n, warps, r, c.sm_count, cps);
+        const int64_t grid = nk_grid(n, warps, r, c.sm_count, cps, a.peer ? kGatherCtas : 0);
         a.x = dx + m0 * k;
         a.y = dy + m0 * n;
         a.mrows = mrows;
         // May this launch overlap what is still running?  Only if nothing it reads is being written
         // and nothing it writes is being read or written.
-        const size_t xbytes = (size_t)mrows * k * 4 * (a.pro == 2 ? 2 : 1), ybytes = (size_t)mrows * n * 4, hbytes = (size_t)k * 4;
-        const bool conflict = a.peer || a.amax || !tuning().overlap_independent || c.untracked_inflight ||
+        const size_t xbytes = (size_t)mrows * k * 4 * (a.pro == 2 ? 2 : 1), hbytes = (size_t)k * 4;
+        const size_t ybytes = a.peer ? 0 : (size_t)mrows * n * 4;  // (a sharded GEMV writes the replicas, which only the gather reads)
+        // (a sharded GEMV's replica stores are ordered by the exchange protocol itself; the first of a
+        // batch always waits: it follows the kernel that advances the epoch word)
+        const bool conflict = (a.peer && (a.peer_j == 0 || !tuning().shard_overlap)) || a.amax || !tuning().overlap_independent || c.untracked_inflight ||
                               c.inflight_reads.size() + c.inflight_writes.size() > kMaxTrackedRanges ||
                               overlaps(c.inflight_writes, a.x, xbytes) || overlaps(c.inflight_writes, a.pro_add, hbytes) ||
                               overlaps(c.inflight_writes, a.y, ybytes) || overlaps(c.inflight_reads, a.y, ybytes) ||

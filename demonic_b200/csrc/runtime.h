@@ -120,6 +120,7 @@ struct Tuning {
     int zero_copy_y = 1;    // host-pointer entry points: kernels store y directly into pinned host memory
     int decode_fused = 1;   // decode step: fuse the companions into the GEMVs / attention (0 = one kernel per op)
     int shard_fused = -1;   // sharded GEMV: 1 = peer stores fused into the kernel, 0 = NCCL all-gather, -1 = by world size
+    int shard_overlap = 1;  // sharded GEMVs of one batch overlap (0 = each waits for the previous exchange's gather)
     int overlap_independent = 1;  // GEMVs that touch nothing a running kernel touches skip their dependency wait
     int wait_limit_us = 0;  // bound of the device-side waits on another rank, microseconds (0 = about one second)
     int timing = 0;         // per-call phase timing printed to stderr (also DMC_CUDA_TIME=1)

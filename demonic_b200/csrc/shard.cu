@@ -113,41 +113,78 @@ void shard_range(int64_t n, int rank, int world, int64_t *r0, int64_t *r1) {
 // remote stores): it runs beside it, and re-reads each pair (bounded) until it carries the epoch of
 // this exchange, then writes the plain y of that epoch's parity.  j: position of the exchange in the
 // current batch of launches; n: rows of the whole y.
-__global__ void __launch_bounds__(256) peer_gather_kernel(const PeerOut *p, int n, int j) {
+//
+// Shape: a few CTAs that fit exactly into the CTA slots the sharded GEMV leaves free for them
+// (kGatherCtas slots: a GEMV CTA is 256 threads x 128 registers, a gather CTA 512 threads x <= 64), so
+// that the gather really is resident beside the GEMV and -- when exchanges overlap -- does not sit in
+// slots the next GEMV needs.  A warp owns chunks of 256 consecutive 16-byte pieces (4 KiB).  Pieces that
+// are neighbours in y are produced by neighbouring warps of the GEMV at about the same time, so one lane
+// per chunk watches the chunk's last piece (re-reading it every ~100 ns), and only when those have
+// arrived are the others read, eight per lane with the loads issued together, usually all there:
+// hundreds of times fewer polling reads than one per piece, which matters because they compete with the
+// weight stream for L2 for as long as the GEMVs run.
+constexpr int kGatherThreads = 512, kGatherChunk = 256;
+int gather_ctas(int64_t n) {
+    const int64_t per_cta = (int64_t)(kGatherThreads / 32) * kGatherChunk;  // pieces one CTA covers in one pass
+    return (int)std::max<int64_t>(1, std::min<int64_t>(kGatherCtas, (n / 2 + per_cta - 1) / per_cta));
+}
+
+__global__ void __launch_bounds__(kGatherThreads, 2) peer_gather_kernel(const PeerOut *p, int n, int j, float *dst_override) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // the epoch word was advanced before any kernel of this batch could start (peer_batch_end_kernel)
     const unsigned e = *(volatile const unsigned *)p->epoch + 1u + (unsigned)j;
     const unsigned long long *src = p->ty[p->rank] + (size_t)(e & 1u) * p->stride;
-    float *dst = p->yplain + (size_t)(e & 1u) * p->stride;
+    float *dst = dst_override ? dst_override : p->yplain + (size_t)(e & 1u) * p->stride;
     const int pairs2 = n / 2;  // 16-byte pieces
     const long long limit = p->wait_cycles;
-    const int first = blockIdx.x * blockDim.x;
-    // While the GEMVs are still streaming, one thread per CTA watches one piece at a relaxed pace, so
-    // that the 32K threads of this grid do not load L2 for the whole duration of the GEMV.
-    if (threadIdx.x == 0 && first < pairs2) {
-        const long long t0 = clock64();
+    __shared__ int s_failed;
+    if (threadIdx.x == 0) s_failed = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int warp = (blockIdx.x * kGatherThreads + threadIdx.x) >> 5, warps = gridDim.x * (kGatherThreads / 32);
+    const long long t0 = clock64();
+    auto load_piece = [&](int i, unsigned &a0, unsigned &a1, unsigned &b0, unsigned &b1) {
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(b0), "=r"(b1) : "l"(src + 2 * (size_t)i) : "memory");
+    };
+    // lane l watches the last piece of this warp's l-th chunk (a timeout is reported by the loop below)
+    for (int c0 = (warp + lane * warps) * kGatherChunk; c0 < pairs2; c0 += 32 * warps * kGatherChunk) {
+        const int watched = min(c0 + kGatherChunk, pairs2) - 1;
         for (;;) {
             unsigned a0, a1, b0, b1;
-            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(b0), "=r"(b1) : "l"(src + 2 * (size_t)first) : "memory");
-            if (a1 == e && b1 == e) break;
-            if (clock64() - t0 > limit) break;  // the loop below reports it
-            __nanosleep(200);
+            load_piece(watched, a0, a1, b0, b1);
+            if ((a1 == e && b1 == e) || clock64() - t0 > limit) break;
+            __nanosleep(100);
         }
     }
-    __syncthreads();
-    for (int i = first + threadIdx.x; i < pairs2; i += gridDim.x * blockDim.x) {
-        unsigned a0, a1, b0, b1;
-        const long long t0 = clock64();
-        for (;;) {
-            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(b0), "=r"(b1) : "l"(src + 2 * (size_t)i) : "memory");
-            if (a1 == e && b1 == e) break;
+    __syncwarp();
+    for (int c0 = warp * kGatherChunk; c0 < pairs2; c0 += warps * kGatherChunk) {
+        constexpr int P = kGatherChunk / 32;
+        unsigned a0[P], a1[P], b0[P], b1[P];
+        unsigned missing = 0u;
+#pragma unroll
+        for (int t = 0; t < P; ++t)
+            if (c0 + t * 32 + lane < pairs2) missing |= 1u << t;
+        // every round re-reads all of the lane's missing pieces at once: one L2 round trip per round,
+        // not one per piece
+        while (missing) {
+#pragma unroll
+            for (int t = 0; t < P; ++t)
+                if (missing >> t & 1u) load_piece(c0 + t * 32 + lane, a0[t], a1[t], b0[t], b1[t]);
+#pragma unroll
+            for (int t = 0; t < P; ++t) {
+                if ((missing >> t & 1u) && a1[t] == e && b1[t] == e) {
+                    *reinterpret_cast<float2 *>(dst + 2 * (size_t)(c0 + t * 32 + lane)) = make_float2(__uint_as_float(a0[t]), __uint_as_float(b0[t]));
+                    missing &= ~(1u << t);
+                }
+            }
+            if (!missing) break;
             if (clock64() - t0 > limit) {  // give up instead of hanging: the host reads the error word
                 *(volatile int *)p->err = 6;
+                s_failed = 1;
                 break;
             }
             __nanosleep(100);
         }
-        *reinterpret_cast<float2 *>(dst + 2 * (size_t)i) = make_float2(__uint_as_float(a0), __uint_as_float(b0));
     }
     if ((n & 1) && blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long v;
@@ -157,11 +194,42 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const PeerOut *p, int 
             if ((unsigned)(v >> 32) == e) break;
             if (clock64() - t0 > limit) {
                 *(volatile int *)p->err = 6;
+                s_failed = 1;
                 break;
             }
             __nanosleep(100);
         }
         dst[n - 1] = __uint_as_float((unsigned)v);
+    }
+    // The CTA that finishes last tells every rank that this rank has read exchange e completely (its
+    // replica buffer may be reused by exchange e + 2).  Publications go out in epoch order, so a
+    // published value e means "every exchange up to e".  A gather that gave up publishes nothing.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    unsigned *cnt = p->gcount + (e & 3u);
+    const unsigned arrived = atomicAdd(cnt, 1u);
+    if (s_failed) atomicOr(p->gcount + 4, 1u << (e & 3u));
+    if (arrived != gridDim.x - 1u) return;
+    *cnt = 0u;
+    const unsigned failed = atomicAnd(p->gcount + 4, ~(1u << (e & 3u))) & (1u << (e & 3u));
+    __threadfence();
+    if (failed) return;
+    const unsigned *own = p->gdone[p->rank] + p->rank;
+    const long long t1 = clock64();
+    while (*(volatile const unsigned *)own != e - 1u) {  // the previous exchange's publication first
+        if (clock64() - t1 > limit) {
+            *(volatile int *)p->err = 8;
+            return;
+        }
+        __nanosleep(100);
+    }
+    for (int i = 0; i < kMaxPeers; ++i) {
+        if (i < p->world) {
+            int r = p->rank + 1 + i;  // own word last: the next local gather's publication waits on it
+            if (r >= p->world) r -= p->world;
+            *(volatile unsigned *)(p->gdone[r] + p->rank) = e;
+        }
     }
 }
 
@@ -179,8 +247,9 @@ __global__ void peer_batch_end_kernel(const PeerOut *p, int count) {
 }
 
 // j: position of this call in a batch of back-to-back sharded GEMVs; end_batch: it is the last one.
+// dst: where the whole y goes on this rank (device, n floats); null = the library's own y buffers.
 int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype, cudaStream_t s,
-                  int j = 0, bool end_batch = true) {
+                  int j = 0, bool end_batch = true, float *dst = nullptr) {
     Shard &sh = g_shard;
     if (!sh.ready) return fail(DMC_CUDA_ERR_BAD_ARG, "shard_gemv: dmc_cuda_shard_init has not been called");
     if (n > sh.max_n) return fail(DMC_CUDA_ERR_UNSUPPORTED, "shard_gemv: n=%lld beyond the max_n=%lld given to shard_init",
@@ -209,13 +278,17 @@ int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, i
         if (rc == DMC_CUDA_OK) {
             const PeerOut *pp = sh.d_peer;
             int rows = (int)n, jj = j;
-            void *params[] = {&pp, &rows, &jj};
-            const int ctas = (int)std::max<int64_t>(1, std::min<int64_t>(128, (n / 2 + 255) / 256));  // one 16-byte piece per thread up to 64K rows
-            rc = launch_ex((const void *)peer_gather_kernel, dim3(ctas), dim3(256), 0, s, params);
+            void *params[] = {&pp, &rows, &jj, &dst};
+            const int ctas = gather_ctas(n);
+            // the gather never waits for its predecessor; what it writes is recorded so that a consumer of y does
+            rc = launch_ex((const void *)peer_gather_kernel, dim3(ctas), dim3(kGatherThreads), 0, s, params,
+                           c.nowait_inflight ? kLaunchOverlap : kLaunchTracked);
+            if (dst) c.inflight_writes.push_back(AddrRange{(uintptr_t)dst, (uintptr_t)dst + (size_t)n * 4});
+            else c.inflight_writes.push_back(AddrRange{(uintptr_t)sh.y, (uintptr_t)sh.y + (size_t)2 * sh.max_n * 4});
             if (rc == DMC_CUDA_OK && end_batch) {
                 int count = j + 1;
                 void *params2[] = {&pp, &count};
-                rc = launch_ex((const void *)peer_batch_end_kernel, dim3(1), dim3(32), 0, s, params2);
+                rc = launch_ex((const void *)peer_batch_end_kernel, dim3(1), dim3(32), 0, s, params2, kLaunchTracked);
             }
         }
         return rc;
@@ -225,6 +298,10 @@ int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, i
     if (rc) return rc;
     if (sh.world == 1) return DMC_CUDA_OK;
     ctx().untracked_inflight = true;  // the collective below writes y outside the launch planner's view
+    struct CopyOut {  // the NCCL exchange fills the library's own y; a caller's destination gets a copy
+        float *dst, *src; int64_t n; cudaStream_t s;
+        ~CopyOut() { if (dst) cudaMemcpyAsync(dst, src, (size_t)n * 4, cudaMemcpyDeviceToDevice, s); }
+    } copy_out{dst, sh.y, n, s};
     if (n % sh.world == 0) {
         DMC_NCCL_TRY(g_nccl.AllGather(sh.y + r0, sh.y, (size_t)(n / sh.world), ncclFloat32, sh.comm, s));
     } else {  // ragged: every rank broadcasts its slice
@@ -345,7 +422,12 @@ int shard_init_locked(int rank, int world, const uint8_t *id128, int64_t max_n) 
             po.ty[r] = reinterpret_cast<unsigned long long *>(static_cast<char *>(sh.peer_base[r]) +
                                                               (size_t)2 * max_n * sizeof(float) + kTailBytes);
         po.yplain = sh.y;
+        // tail of the region: [0] the epoch word, [8..12] the gather's arrival counters + failure mask,
+        // [16..24) the published epochs of every rank's gather (written by the peers)
+        for (int r = 0; r < world; ++r)
+            po.gdone[r] = reinterpret_cast<unsigned *>(static_cast<char *>(sh.peer_base[r]) + (size_t)2 * max_n * sizeof(float)) + 16;
         po.epoch = reinterpret_cast<unsigned *>(sh.region + (size_t)2 * max_n * sizeof(float));
+        po.gcount = po.epoch + 8;
         po.err = ctx().err_word;
         po.stride = max_n;
         // bound of the gather kernel's wait for its peers: "wait_limit_us", by default about a second
@@ -429,9 +511,10 @@ extern "C" int dmc_cuda_shard_probe_timeout(int64_t n) {
         return fail(DMC_CUDA_ERR_BAD_ARG, "shard_probe_timeout: needs dmc_cuda_shard_init with the fused exchange and 1 <= n <= max_n");
     const PeerOut *pp = sh.d_peer;
     int rows = (int)n, far = 1 << 20;  // an epoch a million exchanges ahead: nobody has written it
-    void *params[] = {&pp, &rows, &far};
-    const int ctas = (int)std::max<int64_t>(1, std::min<int64_t>(128, (n / 2 + 255) / 256));
-    int rc = launch_ex((const void *)peer_gather_kernel, dim3(ctas), dim3(256), 0, ctx().stream, params);
+    float *none = nullptr;
+    void *params[] = {&pp, &rows, &far, &none};
+    const int ctas = gather_ctas(n);
+    int rc = launch_ex((const void *)peer_gather_kernel, dim3(ctas), dim3(kGatherThreads), 0, ctx().stream, params);
     if (rc) return rc;
     DMC_CUDA_TRY(cudaStreamSynchronize(ctx().stream));
     stream_drained();
@@ -453,6 +536,18 @@ extern "C" int dmc_cuda_shard_gemv(const void *dW_shard, const float *dx, int64_
     std::lock_guard<std::mutex> lock(ctx_mutex());
     if (dmc::status()) return dmc::status();
     return shard_gemv_on(dW_shard, dx, k, n, wdtype, ctx().stream);
+}
+
+extern "C" int dmc_cuda_shard_gemv_batch(const void *const *dW_shards, int count, const float *dx, float *const *dy_out,
+                                         int64_t k, int64_t n, int wdtype) {
+    std::lock_guard<std::mutex> lock(ctx_mutex());
+    if (dmc::status()) return dmc::status();
+    if (!dW_shards || count < 1) return fail(DMC_CUDA_ERR_BAD_ARG, "shard_gemv_batch: needs count >= 1 weight shards");
+    for (int i = 0; i < count; ++i) {
+        int rc = shard_gemv_on(dW_shards[i], dx, k, n, wdtype, ctx().stream, i, i == count - 1, dy_out ? dy_out[i] : nullptr);
+        if (rc) return rc;
+    }
+    return DMC_CUDA_OK;
 }
 
 extern "C" double dmc_cuda_bench_shard(const void *const *dW_shards, int copies, const float *dx, int64_t k,

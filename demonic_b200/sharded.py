@@ -43,6 +43,16 @@ def gemv(dW_shard: backend.DeviceBuffer, dx: backend.DeviceBuffer, k: int, n: in
     _lib.check()
 
 
+def gemv_batch(dW_shards: list[backend.DeviceBuffer], dx: backend.DeviceBuffer, dys: list[backend.DeviceBuffer] | None,
+               k: int, n: int, wdtype: int = backend.W_BF16) -> None:
+    """``dmc_cuda_shard_gemv_batch``: independent sharded GEMVs of one x; ``dys[i]`` receives the whole y of GEMV i."""
+    arr = (C.c_void_p * len(dW_shards))(*[b.ptr for b in dW_shards])
+    outs = (C.c_void_p * len(dys))(*[b.ptr for b in dys]) if dys is not None else None
+    _lib.load().dmc_cuda_shard_gemv_batch(C.cast(arr, C.c_void_p), len(dW_shards), dx.ptr,
+                                          C.cast(outs, C.c_void_p) if outs is not None else None, k, n, wdtype)
+    _lib.check()
+
+
 def output(n: int) -> np.ndarray:
     """The replicated y (first n floats), copied to the host after a sync."""
     lib = _lib.load()

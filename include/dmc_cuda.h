@@ -290,7 +290,9 @@ int dmc_cuda_shard_path(int world, int peer_access_everywhere, int shard_fused, 
 /* Self-test of the bounded device-side waits: runs the arrival check for an exchange that nobody writes,
  * so every wait in it runs out after "wait_limit_us" and the call returns DMC_CUDA_ERR_TIMEOUT (sticky,
  * like every failure).  Nothing faults or hangs; after dmc_cuda_clear_error() the context works as before.
- * Needs dmc_cuda_shard_init with the fused exchange available (a world of one will do). */
+ * Needs dmc_cuda_shard_init with the fused exchange available (a world of one will do).
+ * (A wait that runs out inside a real exchange is different: the ranks' epochs are then out of step, and the
+ * shard context has to be shut down and initialised again on every rank.) */
 int dmc_cuda_shard_probe_timeout(int64_t n);
 
 /* y = W.x for W[n][k] (k contiguous) of which this rank holds rows dmc_cuda_shard_range(n, rank, world)
@@ -301,6 +303,16 @@ int dmc_cuda_shard_probe_timeout(int64_t n);
  * follows the kernel.  Asynchronous on the context's stream; collective (every rank calls it, in the
  * same order); dx must not alias dmc_cuda_shard_output() of the call before the previous one. */
 int dmc_cuda_shard_gemv(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype);
+
+/* `count` sharded GEMVs of the same x in one batch -- the projections of one activation (q, k, v; gate, up),
+ * each weight row-sharded as above.  dy_out[i] (device, n floats; the array may be null, then only the last two
+ * results are kept, as after single calls) receives the whole y of GEMV i on this rank.  Because the GEMVs of a
+ * batch do not depend on one another, exchange i + 1 streams its weights while the stores of exchange i are
+ * still crossing NVLink; the only ordering kept is the reuse of the two replica buffers (a GEMV checks, with a
+ * bound, that every rank has read the exchange before the previous one).  If x is itself an output still in
+ * flight the GEMVs wait for it as usual.  Collective; asynchronous on the context's stream. */
+int dmc_cuda_shard_gemv_batch(const void *const *dW_shards, int count, const float *dx, float *const *dy_out,
+                              int64_t k, int64_t n, int wdtype);
 float *dmc_cuda_shard_output(void);
 /* The result of the sharded GEMV before the last one (the fused exchange alternates between two
  * buffers; with the NCCL exchange there is only one and this returns it).  Synchronises. */
@@ -359,13 +371,15 @@ const char *dmc_cuda_variant_name(int layout, int wdtype, int variant);
  *   tc_ksplit, tc_smem_kb                                tcgen05 GEMM: K splits, shared-memory ring budget
  *   shard_fused       -1   sharded GEMV: 1 = exchange fused into the kernel, 0 = ncclAllGather, -1 = fused
  *                          whenever every pair of GPUs has peer access
+ *   shard_overlap     1    sharded GEMVs of one batch overlap: only the first waits for the kernel before it, the
+ *                          others start while the previous exchange is still arriving; 0 = one exchange at a time
  *   decode_fused      1    decode step: companions fused into the GEMVs / attention (0 = one kernel per op)
  *   overlap_independent 1  a GEMV that reads nothing a still-running kernel writes (and writes nothing one reads
  *                          or writes) skips its dependency wait and overlaps its predecessors; 0 = every
  *                          kernel waits for the one before it
  *   wait_limit_us     0    bound of device-side waits on another rank, read by dmc_cuda_shard_init (0 = ~1 s);
  *                          a wait that runs out makes the next synchronising call return DMC_CUDA_ERR_TIMEOUT
- *   spin_sync         1    host-pointer builtins poll the stream instead of blocking on it
+ *   spin_sync         0    1 = host-pointer builtins poll the stream instead of blocking on it (measured slower)
  *   timing            0    one line per host-pointer call on stderr: microseconds spent on weights, staging and
  *                          launch, waiting, readback, and the kernel's own time and GB/s (also DMC_CUDA_TIME=1;
  *                          the counterpart of the reference's DMC_GPU_TIME, compiler/src/gpu.rs:45-96) */

@@ -44,6 +44,42 @@ def test_world_of_one_is_the_plain_gemv():
     assert lib.dmc_cuda_status() == 0
 
 
+def test_batch_of_independent_sharded_gemvs_overlaps_and_keeps_every_result():
+    """Six sharded GEMVs of one x in a batch (they may overlap: exchange i + 1 starts while exchange i is
+    still landing; the replica buffer of exchange i is reused by exchange i + 2 under the guard), each
+    with its own destination; then a GEMV that consumes one of the results, which must wait for it."""
+    lib = _lib.load()
+    lib.dmc_cuda_clear_error()
+    n, k = 2048, 2048
+    rng = np.random.default_rng(45)
+    ws = [synth.bf16_weights(rng, (n, k)) for _ in range(6)]
+    x = synth.activations(rng, (k,))
+    lib.dmc_cuda_set_param(b"shard_fused", 1)
+    sharded.init(0, 1, None, n)
+    try:
+        dWs = [backend.DeviceBuffer.from_host(w) for w in ws]
+        dx = backend.DeviceBuffer.from_host(x)
+        dys = [backend.DeviceBuffer(n * 4) for _ in ws]
+        refs = [oracle.gemm_bf16_fma(x.reshape(1, k), np.ascontiguousarray(w.T)).reshape(-1) for w in ws]
+        for rep in range(3):
+            sharded.gemv_batch(dWs, dx, dys, k, n)
+            sharded.gemv(dWs[0], dys[5], k, n)            # x = the last result of the batch: a true dependency
+            backend.sync()
+            for i, (dy, ref) in enumerate(zip(dys, refs)):
+                assert_parity(dy.download(np.float32, n), ref, TOL_BF16, f"rep {rep} batch member {i}")
+            chained = oracle.gemm_bf16_fma(refs[5].reshape(1, k), np.ascontiguousarray(ws[0].T))
+            assert_parity(sharded.output(n), chained, TOL_BF16, f"rep {rep} consumer of a batch result")
+        us = sharded.bench(dWs, dx, k, n, steps=5, warmup=2)
+        assert us > 0
+        sharded.gemv_batch(dWs, dx, None, k, n)
+        assert_parity(sharded.output(n), refs[5], TOL_BF16, "last of a batch without destinations")
+        assert_parity(sharded.output_previous(n), refs[4], TOL_BF16, "the one before it")
+    finally:
+        lib.dmc_cuda_set_param(b"shard_fused", -1)
+        sharded.shutdown()
+    assert lib.dmc_cuda_status() == 0, lib.dmc_cuda_last_error().decode()
+
+
 def test_a_wait_that_runs_out_reports_timeout_and_leaves_the_gpu_usable():
     """The bounded device-side wait, made to run out in the permitted way: the arrival check runs for
     an exchange nobody writes, with a 2 ms limit.  Expected: status 6, nothing delivered, and the next
@@ -149,6 +185,13 @@ for n in (8192, 1001, 1):                   # even split, ragged split, fewer ro
         err = float(np.max(np.abs(y - ref)) / np.max(np.abs(ref)))
         assert err < 1e-5, (rank, n, fused, err)
     lib.dmc_cuda_set_param(b"shard_fused", 1)
+    dys = [backend.DeviceBuffer(n * 4) for _ in range(5)]
+    for rep in range(3):                     # a batch of independent exchanges: adjacent ones overlap
+        sharded.gemv_batch([dW] * 5, dx, dys, k, n)
+        backend.sync()
+        for i, dy in enumerate(dys):
+            y = dy.download(np.float32, n)
+            assert float(np.max(np.abs(y - ref)) / np.max(np.abs(ref))) < 1e-5, ("batch", rank, n, rep, i)
     us = sharded.bench([dW, dW, dW], dx, k, n, steps=5, warmup=2)
     sharded.gemv(dW, dx, k, n)
     for name, y in (("last", sharded.output(n)), ("previous", sharded.output_previous(n))):
