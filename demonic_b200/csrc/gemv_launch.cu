@@ -111,6 +111,61 @@ void note(std::vector<AddrRange> &list, const void *p, size_t bytes) {
 
 }  // namespace
 
+// ---- host-pointer calls: x in and y out without the copy engines --------------------------
+// For the few KiB a GEMV call moves, a copy-engine transfer costs more in start-up than in transfer.
+// Two small kernels move the data instead, chained to the GEMV by programmatic dependent launch:
+// one reads x from the pinned host mirror, 16 bytes per thread, one PCIe round trip in all; the other
+// writes y to the pinned host mirror in full 128-byte lines (the GEMV itself would store it four
+// bytes at a time) and then a sequence number, which the waiting host thread polls in its own memory
+// instead of asking the driver.
+__global__ void __launch_bounds__(1024) dmc_stage_x_kernel(const float *src_host, float *dst, long long elems) {
+    griddep_launch_dependents();  // the GEMV behind this kernel loads its first weights meanwhile
+    griddep_wait();               // whatever used the staging area before is complete
+    const long long nvec = elems / 4;
+    for (long long i = (long long)blockIdx.x * 1024 + threadIdx.x; i < nvec; i += (long long)gridDim.x * 1024)
+        reinterpret_cast<float4 *>(dst)[i] = __ldcv(reinterpret_cast<const float4 *>(src_host) + i);
+    if (blockIdx.x == 0 && threadIdx.x < (int)(elems - nvec * 4)) dst[nvec * 4 + threadIdx.x] = __ldcv(src_host + nvec * 4 + threadIdx.x);
+}
+
+__global__ void __launch_bounds__(1024) dmc_deliver_kernel(const float *src, float *dst_host, long long elems,
+                                                           unsigned *done_word, unsigned seq) {
+    griddep_wait();  // y is complete
+    const long long nvec = elems / 4;
+    for (long long i = threadIdx.x; i < nvec; i += 1024)
+        reinterpret_cast<float4 *>(dst_host)[i] = __ldcg(reinterpret_cast<const float4 *>(src) + i);
+    if (threadIdx.x < (int)(elems - nvec * 4)) dst_host[nvec * 4 + threadIdx.x] = __ldcg(src + nvec * 4 + threadIdx.x);
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        *(volatile unsigned *)done_word = seq;  // last: the host reads y once it sees this
+    }
+}
+
+int launch_stage_x(const float *h_src, float *d_dst, size_t elems, cudaStream_t stream) {
+    Context &c = ctx();
+    long long n = (long long)elems;
+    void *params[] = {&h_src, &d_dst, &n};
+    const unsigned ctas = (unsigned)std::max<size_t>(1, std::min<size_t>(16, (elems / 4 + 1023) / 1024));
+    int rc = launch_ex((const void *)dmc_stage_x_kernel, dim3(ctas), dim3(1024), 0, stream, params, kLaunchTracked);
+    if (rc) return rc;
+    note(c.inflight_writes, d_dst, elems * 4);
+    return DMC_CUDA_OK;
+}
+
+int launch_deliver(const float *d_src, float *h_dst, size_t elems, cudaStream_t stream) {
+    Context &c = ctx();
+    long long n = (long long)elems;
+    unsigned seq = ++c.done_seq;
+    unsigned *word = c.done_word;
+    void *params[] = {&d_src, &h_dst, &n, &word, &seq};
+    int rc = launch_ex((const void *)dmc_deliver_kernel, dim3(1), dim3(1024), 0, stream, params, kLaunchTracked);
+    if (rc) return rc;
+    note(c.inflight_reads, d_src, elems * 4);
+    c.done_is_last = true;
+    return DMC_CUDA_OK;
+}
+
 void stream_drained() {
     Context &c = ctx();
     c.inflight_reads.clear();
@@ -141,6 +196,7 @@ int launch_ex(const void *fn, dim3 grid, dim3 block, size_t smem, cudaStream_t s
     cfg.attrs = attr;
     cfg.numAttrs = nattr;
     DMC_CUDA_TRY(cudaLaunchKernelExC(&cfg, fn, params));
+    c.done_is_last = false;
     if (serialise) stream_drained();  // whatever ran before this kernel is complete when it starts
     if (mode == kLaunchOverlap) c.nowait_inflight = true;
     if (mode == kLaunchUntracked) c.untracked_inflight = true;

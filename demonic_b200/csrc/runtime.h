@@ -73,11 +73,26 @@ struct Context {
 
     // resident weights
     std::unordered_map<FpKey, void *, FpKeyHash> by_fingerprint;
+    // What the last call with a weight at a given host address resolved to.  A hit lets a call launch
+    // first and take the content fingerprint while the GPU runs; the fingerprint is still compared on
+    // every call, and a call whose weight turned out to have changed is repeated the slow way.
+    struct Guess {
+        size_t bytes;
+        FpKey key;
+        void *dev;
+        int layout;
+    };
+    std::unordered_map<uintptr_t, Guess> by_address;
     std::vector<RegisteredRange> registered;
     int64_t resident_bytes = 0;
 
     // error word written by kernels whose bounded waits run out (pinned, device-visible)
     int *err_word = nullptr;
+    // Completion word of the host-pointer calls (pinned): the kernel that delivers a call's y writes the
+    // call's sequence number here last.  done_is_last: nothing has been put on the stream since.
+    unsigned *done_word = nullptr;
+    unsigned done_seq = 0;
+    bool done_is_last = false;
 
     // set by the sharded path around a launch: the NK kernel then stores y into every rank's replica
     const void *peer = nullptr;  // device pointer to a PeerOut
@@ -125,6 +140,7 @@ struct Tuning {
     int wait_limit_us = 0;  // bound of the device-side waits on another rank, microseconds (0 = about one second)
     int timing = 0;         // per-call phase timing printed to stderr (also DMC_CUDA_TIME=1)
     int spin_sync = 0;      // host-pointer entry points poll the stream instead of blocking on it
+    int host_io_kernels = 1; // host-pointer entry points move x and y (up to 64 KiB each) with kernels, not the copy engines
 };
 
 Context &ctx();
@@ -171,6 +187,10 @@ cudaError_t dmc_malloc(void **p, size_t bytes);
 cudaError_t dmc_malloc_host(void **p, size_t bytes);
 // True when DMC_CUDA_INJECT names `what` (comma-separated list).
 bool inject_failure(const char *what);
+// x of a host-pointer call from its pinned mirror to the device, and y from the device to its pinned
+// mirror followed by the call's sequence number in Context::done_word (gemv_launch.cu).
+int launch_stage_x(const float *h_src, float *d_dst, size_t elems, cudaStream_t stream);
+int launch_deliver(const float *d_src, float *h_dst, size_t elems, cudaStream_t stream);
 // Grow the context's split-K scratch (partials in bytes, arrival counters in elements).
 int ensure_scratch(size_t partial_bytes, size_t ncounters);
 

@@ -323,7 +323,8 @@ def test_registered_matrix_is_stored_k_contiguous():
     assert lib.dmc_cuda_launch_count() - before == 1, "one transpose kernel at registration"
     resident = lib.dmc_cuda_resident_count()
     assert_parity(gpu_bf16(x, w, 1, k, n), oracle.gemm_bf16_fma(x, w), TOL_BF16)
-    assert lib.dmc_cuda_launch_count() - before == 2 and lib.dmc_cuda_resident_count() == resident
+    # x in, the GEMV, y out
+    assert lib.dmc_cuda_launch_count() - before == 1 + 3 and lib.dmc_cuda_resident_count() == resident
     # another view of the same bytes is served by content, not from the transposed copy
     assert_parity(gpu_bf16(x[:, :2048], w.reshape(2048, 2048), 1, 2048, 2048),
                   oracle.gemm_bf16_fma(x[:, :2048], w.reshape(2048, 2048)), TOL_BF16)
@@ -344,17 +345,18 @@ def test_small_batch_keeps_f32_rows_on_the_cuda_cores(m):
     x = synth.activations(rng, (m, k))
     out = np.full((m, n), np.nan, F)
     lib = dmc.load()
-    before = lib.dmc_cuda_launch_count()
-    dmc.matmul_bf16_gpu_nt(x, w, out, m, k, n)
-    dmc.matmul_bf16_gpu_nt(x, w, out, m, k, n)                  # the weight is resident now: count this call's launches
-    launches = (lib.dmc_cuda_launch_count() - before) // 2
-    ref = oracle.gemm_bf16_fma(x, np.ascontiguousarray(w.T))
-    err = assert_parity(out, ref, TOL_BF16, f"m={m}")
-    if m <= 8:
-        assert err < 1e-5, f"m={m}: the CUDA-core rows use exact f32 activations (got {err:.2e})"
-        assert launches == 1, "up to 8 rows in one instance: W streamed once"
-    lib.dmc_cuda_set_param(b"tc_min_m", 1 << 20)                # every row count on the CUDA cores
+    lib.dmc_cuda_set_param(b"host_io_kernels", 0)               # count the GEMV launches only: x and y by the copy engines
     try:
+        before = lib.dmc_cuda_launch_count()
+        dmc.matmul_bf16_gpu_nt(x, w, out, m, k, n)
+        dmc.matmul_bf16_gpu_nt(x, w, out, m, k, n)              # the weight is resident now: count this call's launches
+        launches = (lib.dmc_cuda_launch_count() - before) // 2
+        ref = oracle.gemm_bf16_fma(x, np.ascontiguousarray(w.T))
+        err = assert_parity(out, ref, TOL_BF16, f"m={m}")
+        if m <= 8:
+            assert err < 1e-5, f"m={m}: the CUDA-core rows use exact f32 activations (got {err:.2e})"
+            assert launches == 1, "up to 8 rows in one instance: W streamed once"
+        lib.dmc_cuda_set_param(b"tc_min_m", 1 << 20)            # every row count on the CUDA cores
         out2 = np.full((m, n), np.nan, F)
         before = lib.dmc_cuda_launch_count()
         dmc.matmul_bf16_gpu_nt(x, w, out2, m, k, n)
@@ -362,6 +364,7 @@ def test_small_batch_keeps_f32_rows_on_the_cuda_cores(m):
         assert assert_parity(out2, ref, TOL_BF16, f"m={m} cuda cores") < 1e-5
     finally:
         lib.dmc_cuda_set_param(b"tc_min_m", 0)
+        lib.dmc_cuda_set_param(b"host_io_kernels", 1)
 
 
 def test_batched_slices_with_several_rows_run_on_the_gpu():
@@ -523,6 +526,52 @@ def test_tma_ring_kernel(k, n, wdtype):
         lib.dmc_cuda_set_param(b"tma_stage_kb", 0)
 
 
+def test_host_call_moves_x_and_y_with_kernels_and_still_checks_the_weight():
+    """Up to 64 KiB each way, a host-pointer call is three kernels (x in, GEMV, y out + completion word)
+    and launches before it has read the weight's fingerprint.  The fingerprint is still compared on every
+    call: a weight changed in place at the same address gives the new product, never the old one; the
+    copy-engine path ("host_io_kernels" = 0) gives bit-identical results; deferred calls deliver at the flush."""
+    lib = dmc.load()
+    lib.dmc_cuda_drop_resident()
+    k, n = 2048, 1536
+    rng = np.random.default_rng(77)
+    w = synth.bf16_weights(rng, (k, n))
+    x = synth.activations(rng, (1, k))
+    first = gpu_bf16(x, w, 1, k, n)
+    before = lib.dmc_cuda_launch_count()
+    again = gpu_bf16(x, w, 1, k, n)
+    assert lib.dmc_cuda_launch_count() - before == 3
+    assert np.array_equal(first, again)
+    assert_parity(again, oracle.gemm_bf16_fma(x, w), TOL_BF16)
+    # same address, new content (every 4th row, so that the sampled words certainly change)
+    w[::4, :] = synth.bf16_weights(rng, (k // 4, n))
+    changed = gpu_bf16(x, w, 1, k, n)
+    assert_parity(changed, oracle.gemm_bf16_fma(x, w), TOL_BF16)
+    assert not np.array_equal(changed, first)
+    assert np.array_equal(gpu_bf16(x, w, 1, k, n), changed)
+    # many different x at one weight: each call's y belongs to its own x
+    for i in range(8):
+        xi = synth.activations(rng, (1, k))
+        assert_parity(gpu_bf16(xi, w, 1, k, n), oracle.gemm_bf16_fma(xi, w), TOL_BF16, f"call {i}")
+    # the copy-engine path computes the same bits
+    lib.dmc_cuda_set_param(b"host_io_kernels", 0)
+    try:
+        assert np.array_equal(gpu_bf16(x, w, 1, k, n), changed)
+    finally:
+        lib.dmc_cuda_set_param(b"host_io_kernels", 1)
+    # deferred calls: nothing is delivered before the flush, everything after it
+    outs = [np.full((1, n), np.nan, F) for _ in range(3)]
+    xs = [synth.activations(rng, (1, k)) for _ in range(3)]
+    for xi, oi in zip(xs, outs):
+        lib.dmc_matmul_bf16_gpu_batched_deferred(xi.ctypes.data, w.ctypes.data, oi.ctypes.data, 1, k, n, 1, 0, 0)
+    assert all(np.isnan(oi).all() for oi in outs)
+    lib.dmc_matmul_bf16_gpu_flush()
+    _lib.check()
+    for xi, oi in zip(xs, outs):
+        assert_parity(oi, oracle.gemm_bf16_fma(xi, w), TOL_BF16)
+    lib.dmc_cuda_drop_resident()
+
+
 def test_resident_kn_weight_is_stored_k_contiguous_once():
     # a [k, n] weight the row-streaming kernel can take is transposed on the device at upload; later calls reuse it
     lib = dmc.load()
@@ -536,8 +585,8 @@ def test_resident_kn_weight_is_stored_k_contiguous_once():
     assert_parity(gpu_bf16(x, w, 1, k, n), ref, TOL_BF16)
     after_first = lib.dmc_cuda_launch_count()
     assert_parity(gpu_bf16(x, w.copy(), 1, k, n), ref, TOL_BF16)
-    assert after_first - first == 2, "upload = one transpose kernel + one GEMV"
-    assert lib.dmc_cuda_launch_count() - after_first == 1, "second call = one GEMV, no re-upload"
+    assert after_first - first == 2 + 2, "upload = one transpose kernel + one GEMV (+ x in, y out)"
+    assert lib.dmc_cuda_launch_count() - after_first == 1 + 2, "second call = one GEMV, no re-upload"
     assert lib.dmc_cuda_resident_count() == 1
     # the same bytes viewed with another shape are a different resident entry
     assert_parity(gpu_bf16(x[:, :2048], w.reshape(2048, 2048), 1, 2048, 2048),
