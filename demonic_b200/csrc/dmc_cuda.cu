@@ -8,6 +8,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <ctime>
+#include <algorithm>
 
 #include "runtime.h"
 
@@ -215,10 +216,30 @@ static bool overlaps_pending(uintptr_t p, size_t bytes) {
 
 // Wait for the stream and perform every deferred host readback
 // (compiler/src/gpu.rs:306-316 `flush_pending`).
+// Outputs that still sit in the device buffer come over in one piece: they are bump-allocated, so one
+// span covers them -- a kernel (full-line stores + the completion word) up to 128 KiB, else one copy.
+static int deliver_pending_locked() {
+    Context &c = g_ctx;
+    size_t lo = SIZE_MAX, hi = 0;
+    for (PendingReadback &r : c.pending)
+        if (r.on_device) {
+            lo = std::min(lo, (size_t)((const char *)r.src - c.h_y));
+            hi = std::max(hi, (size_t)((const char *)r.src - c.h_y) + r.elems * 4);
+            r.on_device = false;
+        }
+    if (hi <= lo) return DMC_CUDA_OK;
+    if (hi - lo <= (128u << 10)) return launch_deliver((const float *)(c.d_y + lo), (float *)(c.h_y + lo), (hi - lo) / 4, c.stream);
+    DMC_CUDA_TRY(cudaMemcpyAsync(c.h_y + lo, c.d_y + lo, hi - lo, cudaMemcpyDeviceToHost, c.stream));
+    c.done_is_last = false;
+    return DMC_CUDA_OK;
+}
+
 static int flush_locked() {
     Context &c = g_ctx;
     if (!c.ready) return g_status;
     if (c.pending.empty() && c.x_off == 0 && c.y_off == 0) return g_status;
+    int drc = deliver_pending_locked();
+    if (drc) return drc;
     DMC_CUDA_TRY(stream_wait(c.stream));
     stream_drained();
     if (check_device_error()) {  // results of a kernel that gave up are not delivered
@@ -505,10 +526,7 @@ static int run_host_call_locked(const HostCall &h) {
     if (rc) return rc;
     if (timing_events) DMC_CUDA_TRY(cudaEventRecord(c.ev1, c.stream));
     const double t_launched = timing ? now_us() : 0.0;
-    if (deliver) {
-        rc = launch_deliver((const float *)(c.d_y + y_base), (float *)(c.h_y + y_base), y_elems, c.stream);
-        if (rc) return rc;
-    } else if (!zc) {
+    if (!deliver && !zc) {
         DMC_CUDA_TRY(cudaMemcpyAsync(c.h_y + y_base, c.d_y + y_base, y_elems * 4, cudaMemcpyDeviceToHost, c.stream));
         c.done_is_last = false;
     }
@@ -528,7 +546,7 @@ static int run_host_call_locked(const HostCall &h) {
     }
     const double t2 = timing ? now_us() : 0.0;
 
-    c.pending.push_back(PendingReadback{(const float *)(c.h_y + y_base), h.out, y_elems});
+    c.pending.push_back(PendingReadback{(const float *)(c.h_y + y_base), h.out, y_elems, deliver});
     c.x_off = x_base + x_elems * 4;  // (also makes the flush below non-trivial when nothing was deferred)
     if (h.defer) {
         c.y_off = y_base + y_elems * 4;
@@ -540,6 +558,8 @@ static int run_host_call_locked(const HostCall &h) {
     if (!timing) return flush_locked();
     // the flush, taken apart: wait for the stream, then the host copies of every pending output
     const size_t npending = c.pending.size();
+    rc = deliver_pending_locked();
+    if (rc) return rc;
     cudaError_t we = stream_wait(c.stream);
     const double t3 = now_us();
     if (we != cudaSuccess) return fail(DMC_CUDA_ERR_CUDA, "stream wait failed: %s", cudaGetErrorString(we));
@@ -604,6 +624,7 @@ extern "C" void dmc_cuda_shutdown(void) {
     if (c.d_tmpx) cudaFree(c.d_tmpx);
     if (c.err_word) cudaFreeHost(c.err_word);
     if (c.done_word) cudaFreeHost(c.done_word);
+    if (c.deliver_count) cudaFree(c.deliver_count);
     if (c.ingest_ring) cudaFreeHost(c.ingest_ring);
     if (c.ev0) cudaEventDestroy(c.ev0);
     if (c.ev1) cudaEventDestroy(c.ev1);

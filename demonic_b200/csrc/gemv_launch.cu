@@ -128,17 +128,21 @@ __global__ void __launch_bounds__(1024) dmc_stage_x_kernel(const float *src_host
 }
 
 __global__ void __launch_bounds__(1024) dmc_deliver_kernel(const float *src, float *dst_host, long long elems,
-                                                           unsigned *done_word, unsigned seq) {
+                                                           unsigned *done_word, unsigned seq, unsigned *arrived) {
     griddep_wait();  // y is complete
     const long long nvec = elems / 4;
-    for (long long i = threadIdx.x; i < nvec; i += 1024)
+    for (long long i = (long long)blockIdx.x * 1024 + threadIdx.x; i < nvec; i += (long long)gridDim.x * 1024)
         reinterpret_cast<float4 *>(dst_host)[i] = __ldcg(reinterpret_cast<const float4 *>(src) + i);
-    if (threadIdx.x < (int)(elems - nvec * 4)) dst_host[nvec * 4 + threadIdx.x] = __ldcg(src + nvec * 4 + threadIdx.x);
+    if (blockIdx.x == 0 && threadIdx.x < (int)(elems - nvec * 4)) dst_host[nvec * 4 + threadIdx.x] = __ldcg(src + nvec * 4 + threadIdx.x);
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
-        *(volatile unsigned *)done_word = seq;  // last: the host reads y once it sees this
+        // the CTA that arrives last writes the sequence number, after everybody's stores
+        if (atomicAdd(arrived, 1u) == gridDim.x - 1u) {
+            *arrived = 0u;
+            __threadfence_system();
+            *(volatile unsigned *)done_word = seq;  // last: the host reads y once it sees this
+        }
     }
 }
 
@@ -156,10 +160,16 @@ int launch_stage_x(const float *h_src, float *d_dst, size_t elems, cudaStream_t 
 int launch_deliver(const float *d_src, float *h_dst, size_t elems, cudaStream_t stream) {
     Context &c = ctx();
     long long n = (long long)elems;
+    if (!c.deliver_count) {
+        DMC_CUDA_TRY(dmc_malloc((void **)&c.deliver_count, sizeof(unsigned)));
+        DMC_CUDA_TRY(cudaMemset(c.deliver_count, 0, sizeof(unsigned)));
+    }
     unsigned seq = ++c.done_seq;
-    unsigned *word = c.done_word;
-    void *params[] = {&d_src, &h_dst, &n, &word, &seq};
-    int rc = launch_ex((const void *)dmc_deliver_kernel, dim3(1), dim3(1024), 0, stream, params, kLaunchTracked);
+    unsigned *word = c.done_word, *arrived = c.deliver_count;
+    void *params[] = {&d_src, &h_dst, &n, &word, &seq, &arrived};
+    // one CTA per 16 KiB, at most 8: several SMs push a larger y across PCIe faster than one
+    const unsigned ctas = (unsigned)std::max<size_t>(1, std::min<size_t>(8, (elems * 4 + (16u << 10) - 1) / (16u << 10)));
+    int rc = launch_ex((const void *)dmc_deliver_kernel, dim3(ctas), dim3(1024), 0, stream, params, kLaunchTracked);
     if (rc) return rc;
     note(c.inflight_reads, d_src, elems * 4);
     c.done_is_last = true;

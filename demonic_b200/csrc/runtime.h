@@ -41,6 +41,7 @@ struct PendingReadback {
     const float *src;  // pinned staging
     float *dst;        // caller's `out`
     size_t elems;
+    bool on_device;    // y still sits in the device buffer (same offset): the flush brings it to `src`
 };
 
 struct Context {
@@ -93,6 +94,7 @@ struct Context {
     unsigned *done_word = nullptr;
     unsigned done_seq = 0;
     bool done_is_last = false;
+    unsigned *deliver_count = nullptr;  // device: arrival counter of the delivering kernel's CTAs
 
     // set by the sharded path around a launch: the NK kernel then stores y into every rank's replica
     const void *peer = nullptr;  // device pointer to a PeerOut
