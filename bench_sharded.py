@@ -135,21 +135,22 @@ def run(args, rank: int, world: int) -> None:
     alg = synth.gemv_bytes(ROWS, COLS)            # whole job: every weight byte once + x + y
     value = alg * copies / us_max / 1e3
 
-    # end to end: host x in, replicated y out, every step
+    # end to end: host x in, the whole replicated y out in host memory on every rank, every step
+    y_host = np.empty(ROWS, np.float32)
     for _ in range(args.warmup):
-        dx.upload(x)
-        sharded.gemv(bufs[0], dx, COLS, ROWS)
-        sharded.output(ROWS)
+        sharded.gemv_host(bufs[0], x, y_host, COLS, ROWS)
     dist.barrier()
     t0 = time.perf_counter()
     for i in range(args.steps):
-        dx.upload(x)
-        sharded.gemv(bufs[i % copies], dx, COLS, ROWS)
-        sharded.output(ROWS)
+        sharded.gemv_host(bufs[i % copies], x, y_host, COLS, ROWS)
     dt = (time.perf_counter() - t0) / args.steps
+    e2e_err = scaled_err(y_host, y_ref)
     alle = [None] * world
-    dist.all_gather_object(alle, [dt])
+    dist.all_gather_object(alle, [dt, e2e_err])
     dt_max = max(v[0] for v in alle)
+    parity["e2e_host_pointers"] = max(v[1] for v in alle)
+    if not parity["e2e_host_pointers"] <= 1e-2:
+        raise SystemExit(f"bench: e2e: y off by {parity['e2e_host_pointers']:.3e} on some rank (> 1e-2)")
     dist.barrier()
 
     if rank == 0:
@@ -177,7 +178,7 @@ def run(args, rank: int, world: int) -> None:
                          "note": "per GPU: whole-job algorithmic bytes / world / step time (includes the exchange)"},
             "e2e": {"value": alg / dt_max / 1e9, "unit": UNIT, "h2d_bytes_per_step": 4 * COLS,
                     "d2h_bytes_per_step": 4 * ROWS, "ms_per_step": dt_max * 1e3,
-                    "note": "per step and rank: H2D of x, sharded GEMV with its exchange, D2H of the whole y; max over ranks"},
+                    "note": "per step and rank: one synchronous dmc_cuda_shard_gemv_host call (host x in, sharded GEMV with its exchange, the whole y in host memory); max over ranks"},
             "cpu_baseline": None,
             "clocks": clocks.summary(),
             "gpu_launches": launches_per_step * args.steps,

@@ -42,6 +42,7 @@ SIGNATURES = {
     "dmc_cuda_sync": (C.c_int, []),
     "dmc_cuda_gemv_dev": (C.c_int, [VP, VP, VP, I64, I64, I64, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_gemv_bf16_noalloc": (C.c_int, [VP, VP, VP, I64, I64, VP]),
+    "dmc_cuda_shard_gemv_host": (C.c_int, [VP, VP, VP, I64, I64, C.c_int]),
     "dmc_cuda_shard_range": (None, [I64, C.c_int, C.c_int, C.POINTER(I64), C.POINTER(I64)]),
     "dmc_cuda_shard_unique_id": (C.c_int, [VP]),
     "dmc_cuda_shard_init": (C.c_int, [C.c_int, C.c_int, VP, I64]),

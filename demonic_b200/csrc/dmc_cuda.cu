@@ -632,6 +632,44 @@ extern "C" void dmc_cuda_shutdown(void) {
     c = Context();
 }
 
+extern "C" int dmc_cuda_shard_gemv_host(const void *dW_shard, const float *x_host, float *y_host, int64_t k, int64_t n,
+                                        int wdtype) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_status) return g_status;
+    if (!dW_shard || !x_host || !y_host || k < 1 || n < 1)
+        return fail(DMC_CUDA_ERR_BAD_ARG, "shard_gemv_host: null pointer or empty shape (k=%lld n=%lld)", (long long)k, (long long)n);
+    int rc = ensure_init();
+    if (rc) return rc;
+    Context &c = g_ctx;
+    rc = flush_locked();  // deferred calls of the single-GPU path use the same staging buffers
+    if (rc) return rc;
+    rc = grow_pair(&c.h_x, &c.d_x, &c.x_cap, (size_t)k * 4);
+    if (rc) return rc;
+    rc = grow_pair(&c.h_y, &c.d_y, &c.y_cap, (size_t)n * 4);
+    if (rc) return rc;
+    const bool io_kernels = g_tuning.host_io_kernels != 0;
+    memcpy(c.h_x, x_host, (size_t)k * 4);
+    if (io_kernels && (size_t)k * 4 <= (64u << 10)) {
+        rc = launch_stage_x((const float *)c.h_x, (float *)c.d_x, (size_t)k, c.stream);
+        if (rc) return rc;
+    } else {
+        DMC_CUDA_TRY(cudaMemcpyAsync(c.d_x, c.h_x, (size_t)k * 4, cudaMemcpyHostToDevice, c.stream));
+        c.done_is_last = false;
+    }
+    rc = shard_gemv_to_host(dW_shard, (const float *)c.d_x, k, n, wdtype, (float *)c.h_y, c.stream);
+    if (rc) return rc;
+    if (io_kernels) {  // nothing left to copy: only the completion word, behind everything above
+        rc = launch_deliver(nullptr, nullptr, 0, c.stream);
+        if (rc) return rc;
+    }
+    cudaError_t we = stream_wait(c.stream);
+    if (we != cudaSuccess) return fail(DMC_CUDA_ERR_CUDA, "stream wait failed: %s", cudaGetErrorString(we));
+    stream_drained();
+    if (check_device_error()) return g_status;
+    memcpy(y_host, c.h_y, (size_t)n * 4);
+    return DMC_CUDA_OK;
+}
+
 extern "C" int dmc_cuda_status(void) { return dmc::status(); }
 extern "C" const char *dmc_cuda_last_error(void) { return g_msg; }
 extern "C" void dmc_cuda_clear_error(void) {

@@ -193,6 +193,10 @@ bool inject_failure(const char *what);
 // mirror followed by the call's sequence number in Context::done_word (gemv_launch.cu).
 int launch_stage_x(const float *h_src, float *d_dst, size_t elems, cudaStream_t stream);
 int launch_deliver(const float *d_src, float *h_dst, size_t elems, cudaStream_t stream);
+// Sharded GEMV (shard.cu) whose whole y ends up in `h_dst`, pinned host memory the device can write: with
+// the fused exchange the kernel that checks the arrivals writes it there itself; otherwise one copy follows.
+int shard_gemv_to_host(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype, float *h_dst,
+                       cudaStream_t stream);
 // Grow the context's split-K scratch (partials in bytes, arrival counters in elements).
 int ensure_scratch(size_t partial_bytes, size_t ncounters);
 

@@ -323,6 +323,19 @@ int shard_gemv_on(const void *dW_shard, const float *dx, int64_t k, int64_t n, i
 }
 
 }  // namespace
+
+int shard_gemv_to_host(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype, float *h_dst,
+                       cudaStream_t stream) {
+    Shard &sh = g_shard;
+    if (sh.ready && n <= sh.max_n && fused_path_chosen(sh.world, sh.fused_ok, tuning().shard_fused, k, n))
+        return shard_gemv_on(dW_shard, dx, k, n, wdtype, stream, 0, true, h_dst);
+    int rc = shard_gemv_on(dW_shard, dx, k, n, wdtype, stream);
+    if (rc) return rc;
+    DMC_CUDA_TRY(cudaMemcpyAsync(h_dst, sh.y, (size_t)n * 4, cudaMemcpyDeviceToHost, stream));
+    ctx().done_is_last = false;
+    return DMC_CUDA_OK;
+}
+
 }  // namespace dmc
 
 using namespace dmc;

@@ -43,6 +43,16 @@ def gemv(dW_shard: backend.DeviceBuffer, dx: backend.DeviceBuffer, k: int, n: in
     _lib.check()
 
 
+def gemv_host(dW_shard: backend.DeviceBuffer, x: np.ndarray, out: np.ndarray, k: int, n: int,
+              wdtype: int = backend.W_BF16) -> None:
+    """``dmc_cuda_shard_gemv_host``: x and the whole y in host memory, synchronous, collective."""
+    assert x.dtype == np.float32 and out.dtype == np.float32 and x.size >= k and out.size >= n
+    assert x.flags.c_contiguous and out.flags.c_contiguous
+    _lib.load().dmc_cuda_shard_gemv_host(dW_shard.ptr, x.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p),
+                                         k, n, wdtype)
+    _lib.check()
+
+
 def gemv_batch(dW_shards: list[backend.DeviceBuffer], dx: backend.DeviceBuffer, dys: list[backend.DeviceBuffer] | None,
                k: int, n: int, wdtype: int = backend.W_BF16) -> None:
     """``dmc_cuda_shard_gemv_batch``: independent sharded GEMVs of one x; ``dys[i]`` receives the whole y of GEMV i."""

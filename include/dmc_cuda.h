@@ -304,6 +304,13 @@ int dmc_cuda_shard_probe_timeout(int64_t n);
  * same order); dx must not alias dmc_cuda_shard_output() of the call before the previous one. */
 int dmc_cuda_shard_gemv(const void *dW_shard, const float *dx, int64_t k, int64_t n, int wdtype);
 
+/* The same with host pointers, synchronous: x (k floats) is read from host memory and the whole y (n floats)
+ * is in y_host on return, on every rank -- the form a JIT-bound builtin of a multi-process `dmc` would call.
+ * x crosses through the library's pinned staging; with the fused exchange the kernel that checks the
+ * arrivals writes y straight into pinned host memory while the GEMVs still run, and the host waits on a
+ * completion word there.  dmc_cuda_shard_output() does not hold this call's y afterwards.  Collective. */
+int dmc_cuda_shard_gemv_host(const void *dW_shard, const float *x_host, float *y_host, int64_t k, int64_t n, int wdtype);
+
 /* `count` sharded GEMVs of the same x in one batch -- the projections of one activation (q, k, v; gate, up),
  * each weight row-sharded as above.  dy_out[i] (device, n floats; the array may be null, then only the last two
  * results are kept, as after single calls) receives the whole y of GEMV i on this rank.  Because the GEMVs of a
@@ -379,9 +386,13 @@ const char *dmc_cuda_variant_name(int layout, int wdtype, int variant);
  *                          kernel waits for the one before it
  *   wait_limit_us     0    bound of device-side waits on another rank, read by dmc_cuda_shard_init (0 = ~1 s);
  *                          a wait that runs out makes the next synchronising call return DMC_CUDA_ERR_TIMEOUT
+ *   host_io_kernels   1    host-pointer entry points move x and y (up to 64 KiB each) with two small kernels chained
+ *                          to the GEMV and wait on a completion word in pinned memory; 0 = copy engines +
+ *                          cudaStreamSynchronize (results are bit-identical)
  *   spin_sync         0    1 = host-pointer builtins poll the stream instead of blocking on it (measured slower)
  *   timing            0    one line per host-pointer call on stderr: microseconds spent on weights, staging and
- *                          launch, waiting, readback, and the kernel's own time and GB/s (also DMC_CUDA_TIME=1;
+ *                          launch, waiting, readback, and the kernel's own time and GB/s (also DMC_CUDA_TIME=1; 2 = host clock
+ *                          only, without the CUDA events that serialise the kernels;
  *                          the counterpart of the reference's DMC_GPU_TIME, compiler/src/gpu.rs:45-96) */
 int dmc_cuda_set_param(const char *name, int64_t value);
 

@@ -32,6 +32,12 @@ def test_world_of_one_is_the_plain_gemv():
             assert lib.dmc_cuda_shard_uses_fused(k, n) == fused
             sharded.gemv(dW, dx, k, n)
             assert_parity(sharded.output(n), ref, TOL_BF16, f"fused={fused}")
+            for io in (1, 0):               # host pointers in and out: kernels + completion word, or the copy engines
+                lib.dmc_cuda_set_param(b"host_io_kernels", io)
+                out = np.full(n, np.nan, np.float32)
+                sharded.gemv_host(dW, x, out, k, n)
+                assert_parity(out, ref, TOL_BF16, f"host pointers, fused={fused}, host_io_kernels={io}")
+            lib.dmc_cuda_set_param(b"host_io_kernels", 1)
         lib.dmc_cuda_set_param(b"shard_fused", 1)
         us = sharded.bench([dW, dW, dW], dx, k, n, steps=3, warmup=1)      # graph replays advance the epoch on the device
         assert us > 0
@@ -40,6 +46,7 @@ def test_world_of_one_is_the_plain_gemv():
         assert_parity(sharded.output_previous(n), ref, TOL_BF16, "the other buffer of the pair")
     finally:
         lib.dmc_cuda_set_param(b"shard_fused", -1)
+        lib.dmc_cuda_set_param(b"host_io_kernels", 1)
         sharded.shutdown()
     assert lib.dmc_cuda_status() == 0
 
@@ -184,6 +191,11 @@ for n in (8192, 1001, 1):                   # even split, ragged split, fewer ro
         y = sharded.output(n)
         err = float(np.max(np.abs(y - ref)) / np.max(np.abs(ref)))
         assert err < 1e-5, (rank, n, fused, err)
+        for rep in range(2):                 # host pointers in and out (both buffers of the exchange's pair)
+            out = np.full(n, np.nan, np.float32)
+            sharded.gemv_host(dW, x, out, k, n)
+            err = float(np.max(np.abs(out - ref)) / np.max(np.abs(ref)))
+            assert err < 1e-5, ("host pointers", rank, n, fused, rep, err)
     lib.dmc_cuda_set_param(b"shard_fused", 1)
     dys = [backend.DeviceBuffer(n * 4) for _ in range(5)]
     for rep in range(3):                     # a batch of independent exchanges: adjacent ones overlap
