@@ -197,6 +197,10 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float *__restrict
     const int pos = *pos_ptr, len = pos + 1;
     const int t1 = min(len, t0 + chunk);
     const bool owns_new = pos >= t0 && pos < t0 + chunk;
+    // key ranges beyond the current length take no part at all: they leave before the dependency wait,
+    // and the head's arrival counter and merge count only the ranges that hold keys
+    const int active = min(splits, (len + chunk - 1) / chunk);
+    if (z >= active) return;
     float4 k4[KU], v4[KU];
     auto load_batch = [&](int tb) {
 #pragma unroll
@@ -233,16 +237,24 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float *__restrict
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int tb = t0 + warp; tb < t1; tb += 4 * KU) {
         if (tb != t0 + warp) load_batch(tb);
+        // the scores of the batch first: KU independent shuffle reductions overlap, where one key at a
+        // time each would wait for the one before it
+        float sc[KU];
+#pragma unroll
+        for (int u = 0; u < KU; ++u) {
+            if (tb + 4 * u == pos) {
+                k4[u] = reinterpret_cast<const float4 *>(ks)[lane];
+                v4[u] = reinterpret_cast<const float4 *>(vs)[lane];
+            }
+            sc[u] = q4.x * k4[u].x + q4.y * k4[u].y + q4.z * k4[u].z + q4.w * k4[u].w;
+        }
+#pragma unroll
+        for (int u = 0; u < KU; ++u) sc[u] = warp_sum(sc[u]) * scale;
 #pragma unroll
         for (int u = 0; u < KU; ++u) {
             const int t = tb + 4 * u;
             if (t >= t1) break;
-            if (t == pos) {
-                k4[u] = reinterpret_cast<const float4 *>(ks)[lane];
-                v4[u] = reinterpret_cast<const float4 *>(vs)[lane];
-            }
-            float s = q4.x * k4[u].x + q4.y * k4[u].y + q4.z * k4[u].z + q4.w * k4[u].w;
-            s = warp_sum(s) * scale;
+            const float s = sc[u];
             const float mn = fmaxf(m, s);
             const float corr = __expf(m - mn), p = __expf(s - mn);
             l = l * corr + p;
@@ -276,17 +288,21 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float *__restrict
     // last CTA of the head merges the splits (in split order: fixed)
     __threadfence();
     __syncthreads();
-    if (d == 0) s_last = (atomicAdd(&cnt[h], 1u) == (unsigned)splits - 1u);
+    if (d == 0) s_last = (atomicAdd(&cnt[h], 1u) == (unsigned)active - 1u);
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // splits <= 32: one warp holds a (max, sum) pair per lane, the weights e^(m_z - M) go through
-    // shared memory, then every thread sums its dimension with the loads of all splits in flight
+    // splits <= 32.  Every load of the merge goes out at once -- a thread's value of each split and, in
+    // warp 0, one (max, sum) pair per lane -- so the merge costs one round trip to L2, not one per group
+    // of splits; the weights e^(m_z - M) then go through shared memory.
     const float *p = part + (size_t)h * splits * (HD + 2);
     __shared__ float cz[32], Lsum;
+    float pv[32];
+#pragma unroll
+    for (int u = 0; u < 32; ++u) pv[u] = u < active ? __ldcg(&p[(size_t)u * (HD + 2) + d]) : 0.0f;
     if (warp == 0) {
-        const float mz = lane < splits ? __ldcg(&p[(size_t)lane * (HD + 2) + HD]) : -INFINITY;
-        const float lz = lane < splits ? __ldcg(&p[(size_t)lane * (HD + 2) + HD + 1]) : 0.0f;
+        const float mz = lane < active ? __ldcg(&p[(size_t)lane * (HD + 2) + HD]) : -INFINITY;
+        const float lz = lane < active ? __ldcg(&p[(size_t)lane * (HD + 2) + HD + 1]) : 0.0f;
         float Mx = mz;
 #pragma unroll
         for (int o2 = 16; o2 > 0; o2 >>= 1) Mx = fmaxf(Mx, __shfl_xor_sync(0xffffffffu, Mx, o2));
@@ -297,13 +313,8 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const float *__restrict
     }
     __syncthreads();
     float Os = 0.0f;
-    for (int z0 = 0; z0 < splits; z0 += 8) {
-        float v[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = (z0 + u < splits) ? __ldcg(&p[(size_t)(z0 + u) * (HD + 2) + d]) : 0.0f;
-#pragma unroll
-        for (int u = 0; u < 8; ++u) Os += v[u] * cz[(z0 + u) & 31];
-    }
+    for (int u = 0; u < 32; ++u) Os += pv[u] * cz[u];  // (split order: fixed; absent splits have weight 0)
     out[(size_t)h * HD + d] = Lsum > 0.0f ? Os / Lsum : 0.0f;
     if (d == 0) cnt[h] = 0u;
 }
