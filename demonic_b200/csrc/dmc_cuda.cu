@@ -792,6 +792,7 @@ static int apply_param(const char *name, int64_t value) {
     else if (!strcmp(name, "kn_ctas_per_sm")) t.kn_ctas_per_sm = (int)value;
     else if (!strcmp(name, "kn_ksplit")) t.kn_ksplit = (int)value;
     else if (!strcmp(name, "nk_ctas_per_sm")) t.nk_ctas_per_sm = (int)value;
+    else if (!strcmp(name, "nk_even_rounds")) t.nk_even_rounds = (int)value;
     else if (!strcmp(name, "tma_ring_kb")) t.tma_ring_kb = (int)value;
     else if (!strcmp(name, "tma_stage_kb")) t.tma_stage_kb = (int)value;
     else if (!strcmp(name, "tma_ctas_per_sm")) t.tma_ctas_per_sm = (int)value;

@@ -428,13 +428,30 @@ int launch_nk_tma(const TmaPlan &p, const void *dW, const float *dx, float *dy, 
 // Grid of the NK kernel: one row group per warp when the whole matrix then fits in one wave of
 // resident CTAs (no warp idles, no CTA loops); otherwise exactly SMs x resident CTAs, every CTA
 // owning the same share of the row groups (the kernel splits them evenly by block index).
-int64_t nk_grid(int64_t n, int warps, int r, int sm_count, int cps, int reserve = 0) {
+int64_t nk_grid(int64_t n, int warps, int r, int sm_count, int cps, int reserve = 0, int even_rounds = 0) {
     const int64_t groups = (n + r - 1) / r;
     const int64_t exact = (groups + warps - 1) / warps;
     const int64_t slots = std::max<int64_t>(1, (int64_t)sm_count * cps - reserve);
     // (when the groups do not even fill one CTA per SM, one group per warp still wins: measured at
     // 4096x4096 with 8 rows of x, 64 full CTAs 10.8 us against 148 CTAs with idle warps 17.0 us)
-    return std::max<int64_t>(1, exact <= slots ? exact : slots);
+    if (exact <= slots) return std::max<int64_t>(1, exact);
+    // More groups than warps: with `slots` CTAs most warps own rounds - 1 groups and the rest own
+    // `rounds`, and those finish the kernel with most of the machine idle.  When they are a minority,
+    // fewer CTAs in which every warp owns (all but) exactly `rounds` groups are faster, although fewer
+    // CTAs are resident (never below slots * (rounds - 1) / rounds; the stream needs ~8 MB in flight and
+    // a CTA holds 64 KB).  Measured on B200, slots -> even, independent / dependent launches, us:
+    //   14336x4096 (3 % of the warps own the extra group)  18.05 -> 17.09 / 20.48 -> 18.92
+    //    6144x2048 (30 %)                                    5.22 ->  3.88 /  5.76 ->  5.80
+    //   11264x2048 (38 %)                                    7.44 ->  6.95 /  9.10 ->  8.61
+    //   11008x4096 (32 %)                                   14.04 -> 13.65 / 15.50 -> 15.67
+    //    8192x8192 (73 %)                                   20.43 -> 20.65 / 21.73 -> 22.01
+    //   32000x2048 (76 %)                                   19.38 -> 19.29 / 21.09 -> 20.84
+    const int64_t warps_total = slots * warps;
+    const int64_t rounds = (groups + warps_total - 1) / warps_total;
+    const int64_t in_last_round = groups - (rounds - 1) * warps_total;  // warps that own `rounds` groups
+    const bool even = even_rounds == 2 || (even_rounds == 1 && 2 * in_last_round < warps_total);
+    if (!even) return slots;
+    return std::min(slots, (groups + rounds * warps - 1) / (rounds * warps));
 }
 
 int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, int64_t n,
@@ -519,7 +536,6 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
         }
         int cps = it->second;
         if (tuning().nk_ctas_per_sm > 0) cps = std::min(cps, tuning().nk_ctas_per_sm);
-        const int64_t grid = nk_grid(n, warps, r, c.sm_count, cps, a.peer ? kGatherCtas : 0);
         a.x = dx + m0 * k;
         a.y = dy + m0 * n;
         a.mrows = mrows;
@@ -535,6 +551,7 @@ int launch_nk(const void *dW, const float *dx, float *dy, int64_t m, int64_t k, 
                               overlaps(c.inflight_writes, a.y, ybytes) || overlaps(c.inflight_reads, a.y, ybytes) ||
                               overlaps(c.inflight_writes, a.pro_hout, hbytes) || overlaps(c.inflight_reads, a.pro_hout, hbytes);
         a.nowait = conflict ? 0 : 1;
+        const int64_t grid = nk_grid(n, warps, r, c.sm_count, cps, a.peer ? kGatherCtas : 0, tuning().nk_even_rounds);
         void *params[] = {&a};
         int rc = launch_ex((const void *)fn, dim3((unsigned)grid), dim3(warps * 32), smem, stream, params,
                            conflict ? kLaunchTracked : kLaunchOverlap);
@@ -562,7 +579,7 @@ int timeline_nk(const void *const *dWs, int count, const float *dx, float *dy, i
         return -fail(DMC_CUDA_ERR_UNSUPPORTED, "timeline: needs k %% 8 == 0, a row of x that fits shared memory, count >= 1");
     const void *fn = (const void *)dmc_wrows_kernel<8, 2, 8, 1, uint16_t, true>;
     DMC_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNkMaxSmem));
-    const int64_t grid = nk_grid(n, 8, 2, c.sm_count, 2);
+    const int64_t grid = nk_grid(n, 8, 2, c.sm_count, 2, 0, tuning().nk_even_rounds);
     if ((int64_t)count * grid * 8 > stamps_cap_words) return -fail(DMC_CUDA_ERR_BAD_ARG, "timeline: stamp buffer too small");
     unsigned long long *d_st = nullptr;
     const size_t bytes = (size_t)count * grid * 8 * sizeof(unsigned long long);

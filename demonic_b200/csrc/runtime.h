@@ -126,6 +126,7 @@ struct Tuning {
     int kn_ctas_per_sm = 0; // 0 = per-variant default
     int kn_ksplit = 0;      // 0 = derive from kn_ctas_per_sm
     int nk_ctas_per_sm = 0; // 0 = per-variant default
+    int nk_even_rounds = 1; // row kernel, more row groups than warps: 1 = fewer CTAs with equal shares when few warps would own an extra group, 2 = always, 0 = always all CTA slots
     int tma_ring_kb = 0;    // shared-memory ring per CTA (0 = 96 KiB)
     int tma_stage_kb = 0;   // target stage size (0 = 32 KiB)
     int tma_ctas_per_sm = 0;

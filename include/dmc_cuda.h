@@ -370,6 +370,9 @@ const char *dmc_cuda_variant_name(int layout, int wdtype, int variant);
  * "name=value,name=value"); unknown names return DMC_CUDA_ERR_BAD_ARG.
  *   pdl               1    programmatic dependent launch between the library's kernels
  *   kn_ctas_per_sm, kn_ksplit, nk_ctas_per_sm            0 = the library's choice per shape
+ *   nk_even_rounds    1    row kernel with more row groups than warps: 1 = when fewer than half of the warps would own
+ *                          one group more than the others, launch fewer CTAs in which every warp owns the same
+ *                          number (no ragged end); 2 = always; 0 = always every CTA slot
  *   nk_default        -1   NK kernel configuration used when a call passes variant -1
  *   tma_ring_kb, tma_stage_kb, tma_ctas_per_sm           shape of the TMA ring kernel (0 = default)
  *   store_nk          1    keep resident [k, n] weights k-contiguous on the device
