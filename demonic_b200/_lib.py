@@ -53,6 +53,7 @@ SIGNATURES = {
     "dmc_cuda_shard_output_previous": (VP, []),
     "dmc_cuda_shard_uses_fused": (C.c_int, [I64, I64]),
     "dmc_cuda_shard_probe_timeout": (C.c_int, [I64]),
+    "dmc_cuda_row_kernel_grid": (I64, [I64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_shard_path": (C.c_int, [C.c_int, C.c_int, C.c_int, I64, I64]),
     "dmc_cuda_bench_shard": (C.c_double, [VP, C.c_int, VP, I64, I64, C.c_int, C.c_int, C.c_int, C.c_int]),
     "dmc_cuda_gemm_dev": (C.c_int, [VP, VP, VP, I64, I64, I64, C.c_int]),

@@ -659,6 +659,12 @@ int launch_gemv(const void *dW, const float *dx, float *dy, int64_t m, int64_t k
 
 }  // namespace dmc
 
+extern "C" int64_t dmc_cuda_row_kernel_grid(int64_t n, int warps, int rows_per_warp, int sm_count, int ctas_per_sm,
+                                            int reserved_ctas, int even_rounds) {
+    if (n < 1 || warps < 1 || rows_per_warp < 1 || sm_count < 1 || ctas_per_sm < 1 || reserved_ctas < 0) return 0;
+    return dmc::nk_grid(n, warps, rows_per_warp, sm_count, ctas_per_sm, reserved_ctas, even_rounds);
+}
+
 extern "C" int dmc_cuda_variant_count(int layout, int wdtype) {
     (void)wdtype;
     return layout == DMC_LAYOUT_KN ? dmc::kKnCount : layout == DMC_LAYOUT_NK ? dmc::kNkTotal : 0;

@@ -362,6 +362,13 @@ double dmc_decoder_bench(void *dec, int token, int pos, int steps, int warmup);
 int64_t dmc_decoder_launches_per_step(void *dec);
 void dmc_decoder_destroy(void *dec);
 
+/* CTAs the row kernel is launched with for an n-row matrix (pure arithmetic, no device): `warps` warps per CTA
+ * of `rows_per_warp` rows each, sm_count * ctas_per_sm resident CTA slots of which `reserved_ctas` stay free
+ * (the sharded path keeps room for its arrival check), `even_rounds` as the knob "nk_even_rounds".  One group
+ * of rows per warp while that fits; else every slot, or fewer CTAs with equal shares (see the knob). */
+int64_t dmc_cuda_row_kernel_grid(int64_t n, int warps, int rows_per_warp, int sm_count, int ctas_per_sm,
+                                 int reserved_ctas, int even_rounds);
+
 /* Number of kernel configurations a layout/type offers, and a printable name. */
 int dmc_cuda_variant_count(int layout, int wdtype);
 const char *dmc_cuda_variant_name(int layout, int wdtype, int variant);
