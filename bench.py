@@ -13,7 +13,7 @@ line.  `--impl reference` times the reference's CPU kernel (restated in oracle/,
 the reference being a Rust crate that cannot be built here) on the same workload
 and prints the same line shape.
 
-    python bench.py --case 4096x4096 [--layout nk|kn] [--launches L] [--m M] [--op O] [--decode S]
+    python bench.py --case 4096x4096 [--layout nk|kn] [--launches L] [--m M] [--op O] [--decode S] [--e2e C]
 
 runs one small fixed case and prints its device time: the command profilers are
 pointed at (a few launches of one shape over rotating weight copies, a few hundred
@@ -505,6 +505,23 @@ def run_case(args) -> None:
     if args.timeline:
         run_timeline(args, lib, backend, synth, rows, cols, rng)
         return
+    if args.e2e:
+        # host-pointer calls through the symbol the JIT binds: [k, n] host weight, host x and out
+        w_kn = synth.bf16_weights(rng, (cols, rows))
+        x = synth.activations(rng, (1, cols))
+        out = np.empty((1, rows), np.float32)
+        ax, aw, ao = x.ctypes.data, w_kn.ctypes.data, out.ctypes.data
+        for _ in range(3):
+            lib.dmc_matmul_bf16_gpu(ax, aw, ao, 1, cols, rows)
+        launches0 = lib.dmc_cuda_launch_count()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e):
+            lib.dmc_matmul_bf16_gpu(ax, aw, ao, 1, cols, rows)
+        dt = (time.perf_counter() - t0) / args.e2e
+        assert lib.dmc_cuda_status() == 0, lib.dmc_cuda_last_error().decode()
+        print(f"{args.case} e2e: {dt * 1e6:.1f} us per dmc_matmul_bf16_gpu call, "
+              f"{(lib.dmc_cuda_launch_count() - launches0) // args.e2e} kernel launches per call")
+        return
     w = synth.bf16_weights(rng, (rows, cols))
     x = synth.bf16_weights(rng, (args.m, cols)) if args.op == 1 else synth.activations(rng, (args.m, cols))
     copies = max(2, -(-(args.mib << 20) // w.nbytes))
@@ -567,6 +584,7 @@ def main() -> None:
     ap.add_argument("--mib", type=int, default=256, help="--case: distinct weight bytes to rotate over")
     ap.add_argument("--m", type=int, default=1, help="--case: activation rows")
     ap.add_argument("--op", type=int, default=0, help="--case: 0 GEMV kernels, 1 tcgen05 GEMM (bf16 x), 2 tcgen05 GEMM (f32 x)")
+    ap.add_argument("--e2e", type=int, default=0, help="--case: run this many host-pointer calls (dmc_matmul_bf16_gpu) on the shape instead")
     ap.add_argument("--decode", type=int, default=0, help="--case: run this many decode steps of the benchmark model instead")
     ap.add_argument("--param", action="append", default=[], help="--case: tuning knob name=value")
     ap.add_argument("--timeline", action="store_true", help="--case: per-CTA time stamps of a chain of GEMVs of this shape")

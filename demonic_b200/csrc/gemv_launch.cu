@@ -134,12 +134,17 @@ __global__ void __launch_bounds__(1024) dmc_deliver_kernel(const float *src, flo
     for (long long i = (long long)blockIdx.x * 1024 + threadIdx.x; i < nvec; i += (long long)gridDim.x * 1024)
         reinterpret_cast<float4 *>(dst_host)[i] = __ldcg(reinterpret_cast<const float4 *>(src) + i);
     if (blockIdx.x == 0 && threadIdx.x < (int)(elems - nvec * 4)) dst_host[nvec * 4 + threadIdx.x] = __ldcg(src + nvec * 4 + threadIdx.x);
-    __threadfence_system();
+    // One thread per CTA fences, after the barrier through which it has observed the whole CTA's stores
+    // (fences are cumulative): one PCIe round trip, and with a single CTA no arrival counter at all.
     __syncthreads();
     if (threadIdx.x == 0) {
-        // the CTA that arrives last writes the sequence number, after everybody's stores
-        if (atomicAdd(arrived, 1u) == gridDim.x - 1u) {
-            *arrived = 0u;
+        bool last = true;
+        if (gridDim.x > 1) {
+            __threadfence_system();
+            last = atomicAdd(arrived, 1u) == gridDim.x - 1u;  // the CTA that arrives last writes the sequence number
+            if (last) *arrived = 0u;
+        }
+        if (last) {
             __threadfence_system();
             *(volatile unsigned *)done_word = seq;  // last: the host reads y once it sees this
         }
@@ -167,8 +172,8 @@ int launch_deliver(const float *d_src, float *h_dst, size_t elems, cudaStream_t 
     unsigned seq = ++c.done_seq;
     unsigned *word = c.done_word, *arrived = c.deliver_count;
     void *params[] = {&d_src, &h_dst, &n, &word, &seq, &arrived};
-    // one CTA per 16 KiB, at most 8: several SMs push a larger y across PCIe faster than one
-    const unsigned ctas = (unsigned)std::max<size_t>(1, std::min<size_t>(8, (elems * 4 + (16u << 10) - 1) / (16u << 10)));
+    // one CTA per 64 KiB: a single CTA needs no arrival counter (one fence, then the word)
+    const unsigned ctas = (unsigned)std::max<size_t>(1, std::min<size_t>(8, (elems * 4 + (64u << 10) - 1) / (64u << 10)));
     int rc = launch_ex((const void *)dmc_deliver_kernel, dim3(ctas), dim3(1024), 0, stream, params, kLaunchTracked);
     if (rc) return rc;
     note(c.inflight_reads, d_src, elems * 4);
