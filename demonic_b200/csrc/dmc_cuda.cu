@@ -567,7 +567,7 @@ static int run_host_call_locked(const HostCall &h) {
     const double t4 = now_us();
     float kms = 0.0f;
     if (timing_events) cudaEventElapsedTime(&kms, c.ev0, c.ev1);
-    else fprintf(stderr, "[dmc_cuda time] host clock only: x staged + weight found %.1f us, GEMV launched %.1f us, y delivery launched + fingerprint compared %.1f us\n",
+    else fprintf(stderr, "[dmc_cuda time] host clock only: x staged + weight found %.1f us, GEMV launched %.1f us, fingerprint compared %.1f us (the delivery of y is launched by the flush and counted in the wait)\n",
                  t1 - t0, t_launched - t1, t2 - t_launched);
     const double bytes = (double)w_elems * wsz + 4.0 * x_elems + 4.0 * y_elems;
     fprintf(stderr,
