@@ -135,7 +135,7 @@ struct Tuning {
     int tc_ksplit = 0;      // tcgen05 GEMM: K splits (0 = derive from the tile count)
     int tc_smem_kb = 0;     // tcgen05 GEMM: shared-memory ring budget per CTA
     int tc_min_m = 0;       // activation rows from which `@` goes to the tensor cores (0 = library default)
-    int zero_copy_y = 1;    // host-pointer entry points: kernels store y directly into pinned host memory
+    int zero_copy_y = 1;    // host-pointer entry points with host_io_kernels = 0: kernels store y directly into pinned host memory
     int decode_fused = 1;   // decode step: fuse the companions into the GEMVs / attention (0 = one kernel per op)
     int shard_fused = -1;   // sharded GEMV: 1 = peer stores fused into the kernel, 0 = NCCL all-gather, -1 = by world size
     int shard_overlap = 1;  // sharded GEMVs of one batch overlap (0 = each waits for the previous exchange's gather)

@@ -383,7 +383,8 @@ const char *dmc_cuda_variant_name(int layout, int wdtype, int variant);
  *   nk_default        -1   NK kernel configuration used when a call passes variant -1
  *   tma_ring_kb, tma_stage_kb, tma_ctas_per_sm           shape of the TMA ring kernel (0 = default)
  *   store_nk          1    keep resident [k, n] weights k-contiguous on the device
- *   zero_copy_y       1    host-pointer entry points: kernels store y straight into pinned host memory
+ *   zero_copy_y       1    only with host_io_kernels = 0: the GEMV stores y (up to 64 KiB) straight into pinned host
+ *                          memory instead of a device buffer followed by a copy
  *   tc_min_m          0    activation rows from which `@` goes to the tensor cores (0 = library default)
  *   tc_ksplit, tc_smem_kb                                tcgen05 GEMM: K splits, shared-memory ring budget
  *   shard_fused       -1   sharded GEMV: 1 = exchange fused into the kernel, 0 = ncclAllGather, -1 = fused
